@@ -1,0 +1,414 @@
+// Attention forward for sm_100a: O = softmax(Q K^T * scale + causal mask) V, plus the per-row
+// base-2 log-sum-exp that the column-score pass consumes.
+//
+// Replaces the kernel the Asuka pipeline generates for Attn.forward (cases/kernels/attn.py:18-34):
+// f32 exp2-based softmax with the division deferred until after P.V, P rounded to the input type
+// for the second product, f32 accumulation, fully masked tiles skipped (the numerics fixed by
+// LowerComplexReduce / RecoverTypeInKernel / ReplaceExpAndLog / EquivalentTransform / DynamicFor).
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong through the
+// tensor pipe so that the softmax of one overlaps the MMAs of the other.
+//   warp 0        TMA producer: Q once, then K/V tiles of 128 keys through a 2-stage ring
+//   warp 1        issues tcgen05.mma: S_t = Q_t K^T (SMEM x SMEM), O_t += P_t V (TMEM x SMEM)
+//   warps 4-7     softmax of tile 0: one thread per query row, whole row of S in registers
+//   warps 8-11    softmax of tile 1
+// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 f32 columns each; P_t (16-bit, 64 columns)
+// overwrites the front of S_t once S_t is in registers.  The running maximum is only refreshed
+// when it grows by more than 2^8, so O is rescaled (a TMEM round trip) almost never.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace asuka {
+using namespace sm100;
+
+namespace {
+
+constexpr int kTile = 128;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;  // one [128 x 128] 16-bit tile = two swizzled halves
+constexpr uint32_t kHalfBytes = kTileBytes / 2;
+constexpr int kStages = 2;
+constexpr int kThreads = 384;
+constexpr uint32_t kSmemBytes = (2 + 2 * kStages) * kTileBytes + 1024;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdParams {
+  int B, H, Sq, Skv;
+  int causal, diag_off;
+  int nq_blocks;
+  float scale_log2;
+  float* lse2;
+  uint32_t* status;
+};
+
+struct Bars {
+  uint64_t q_full[2];
+  uint64_t k_full[kStages], k_empty[kStages];
+  uint64_t v_full[kStages], v_empty[kStages];
+  uint64_t s_full[2], p_ready[2], o_done[2], epi[2];
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool kBF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__device__ __forceinline__ void record_timeout(uint32_t* status, uint32_t site) {
+  atomicAdd(&status[0], 1u);
+  status[1] = site;
+}
+
+// number of 128-key tiles query tile [q0, q0+128) has to visit
+__device__ __forceinline__ int kv_tiles_for(int q0, const FwdParams& p) {
+  if (q0 >= p.Sq) return 0;
+  int last = p.Skv - 1;
+  if (p.causal) {
+    int qlast = min(q0 + kTile - 1, p.Sq - 1);
+    last = min(last, qlast + p.diag_off);
+  }
+  return last / kTile + 1;
+}
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) Bars bars;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_s;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base;                          // 2 tiles
+  const uint32_t sK = smem_base + 2 * kTileBytes;         // kStages tiles
+  const uint32_t sV = sK + kStages * kTileBytes;          // kStages tiles
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  volatile uint32_t* abortp = &abort_s;
+
+  // work item: heaviest (latest) query blocks first
+  const int bh_count = p.B * p.H;
+  const int qb = p.nq_blocks - 1 - static_cast<int>(blockIdx.x) / bh_count;
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int b = bh / p.H, h = bh % p.H;
+  const int q0[2] = {qb * 2 * kTile, qb * 2 * kTile + kTile};
+  const int n_kv[2] = {kv_tiles_for(q0[0], p), kv_tiles_for(q0[1], p)};
+  const int n_max = max(n_kv[0], n_kv[1]);
+
+  if (tid == 0) {
+    abort_s = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.q_full[i]), 1);
+      mbar_init(smem_u32(&bars.s_full[i]), 1);
+      mbar_init(smem_u32(&bars.p_ready[i]), 128);
+      mbar_init(smem_u32(&bars.o_done[i]), 1);
+      mbar_init(smem_u32(&bars.epi[i]), 128);
+    }
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(smem_u32(&bars.k_full[i]), 1);
+      mbar_init(smem_u32(&bars.k_empty[i]), 1);
+      mbar_init(smem_u32(&bars.v_full[i]), 1);
+      mbar_init(smem_u32(&bars.v_empty[i]), 1);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_o);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      for (int t = 0; t < 2; ++t) {
+        if (n_kv[t] > 0) {
+          const uint32_t bar = smem_u32(&bars.q_full[t]);
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d(sQ + t * kTileBytes, &map_q, bar, 0, h, q0[t], b);
+          tma_load_4d(sQ + t * kTileBytes + kHalfBytes, &map_q, bar, 64, h, q0[t], b);
+        }
+      }
+      int issued = 0;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j % kStages;
+        const uint32_t use = static_cast<uint32_t>(j / kStages);
+        if (use > 0) {
+          ok = mbar_wait(smem_u32(&bars.k_empty[st]), (use - 1) & 1, abortp);
+          if (!ok) { record_timeout(p.status, 1); break; }
+        }
+        {
+          const uint32_t bar = smem_u32(&bars.k_full[st]);
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, h, j * kTile, b);
+          tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
+        }
+        if (use > 0) {
+          ok = mbar_wait(smem_u32(&bars.v_empty[st]), (use - 1) & 1, abortp);
+          if (!ok) { record_timeout(p.status, 2); issued = j; break; }
+        }
+        {
+          const uint32_t bar = smem_u32(&bars.v_full[st]);
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, h, j * kTile, b);
+          tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, h, j * kTile, b);
+        }
+        issued = j + 1;
+      }
+      if (!ok) {
+        // give copies already in flight a bounded chance to land before the CTA retires
+        volatile uint32_t none = 0;
+        for (int j = max(0, issued - kStages); j < issued; ++j) {
+          mbar_wait(smem_u32(&bars.k_full[j % kStages]), (j / kStages) & 1, &none);
+          mbar_wait(smem_u32(&bars.v_full[j % kStages]), (j / kStages) & 1, &none);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+      constexpr uint32_t idesc_qk = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
+      constexpr uint32_t idesc_pv = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_MN_MAJOR, 128, 128);
+      bool ok = true;
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (n_kv[t] > 0) {
+          ok = mbar_wait(smem_u32(&bars.q_full[t]), 0, abortp);
+          if (!ok) record_timeout(p.status, 3);
+        }
+      }
+      for (int j = 0; j <= n_max && ok; ++j) {
+        const int st = j % kStages;
+        if (j < n_max) {
+          ok = mbar_wait(smem_u32(&bars.k_full[st]), (j / kStages) & 1, abortp);
+          if (!ok) { record_timeout(p.status, 4); break; }
+        }
+        const int jp = j - 1;  // the tile whose P.V is issued in this iteration
+        const int stp = (jp + kStages) % kStages;
+        if (jp >= 0) {
+          ok = mbar_wait(smem_u32(&bars.v_full[stp]), (jp / kStages) & 1, abortp);
+          if (!ok) { record_timeout(p.status, 5); break; }
+        }
+        tc_fence_after_sync();
+        for (int t = 0; t < 2 && ok; ++t) {
+          const uint32_t tS = tbase + t * 128;          // S_t, and P_t in its first 64 columns
+          const uint32_t tO = tbase + 256 + t * 128;    // O_t
+          if (jp >= 0 && jp < n_kv[t]) {
+            ok = mbar_wait(smem_u32(&bars.p_ready[t]), jp & 1, abortp);
+            if (!ok) { record_timeout(p.status, 6); break; }
+            tc_fence_after_sync();
+            const uint64_t vdesc = umma_smem_desc_sw128(sV + stp * kTileBytes, kHalfBytes, 1024);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              umma_ts(tO, tS + kk * 8, vdesc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
+                      (jp > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&bars.o_done[t]));
+          }
+          if (j < n_kv[t]) {
+            const uint64_t qdesc = umma_smem_desc_sw128(sQ + t * kTileBytes, 16, 1024);
+            const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+              umma_ss(tS, qdesc + off, kdesc + off, idesc_qk, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&bars.s_full[t]));
+          }
+        }
+        if (!ok) break;
+        if (j < n_max) umma_commit(smem_u32(&bars.k_empty[st]));
+        if (jp >= 0) umma_commit(smem_u32(&bars.v_empty[stp]));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int t = (warp - 4) >> 2;
+    const int wq = warp & 3;                     // TMEM lane quarter this warp may touch
+    const int r_in_tile = wq * 32 + lane;
+    const int row = q0[t] + r_in_tile;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t tS = tbase + lane_base + t * 128;
+    const uint32_t tO = tbase + lane_base + 256 + t * 128;
+    const int n_t = n_kv[t];
+    const float scale = p.scale_log2;
+    int lim = p.Skv - 1;
+    if (p.causal) lim = min(lim, row + p.diag_off);
+    const int tile_min_lim = p.causal ? min(p.Skv - 1, q0[t] + p.diag_off) : p.Skv - 1;
+
+    float m_ref = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_t; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[t]), j & 1, abortp));
+      if (!ok) { if (lane == 0) record_timeout(p.status, 7); break; }
+      tc_fence_after_sync();
+      float s[128];
+      {
+        uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(s);
+        tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
+        tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
+        tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&u[64]));
+        tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&u[96]));
+        tmem_wait_ld();
+      }
+      if (j * kTile + kTile - 1 > tile_min_lim) {
+        const int thr = lim - j * kTile;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) s[c] = (c > thr) ? -INFINITY : s[c];
+      }
+      float m_tile = s[0];
+#pragma unroll
+      for (int c = 1; c < 128; ++c) m_tile = fmaxf(m_tile, s[c]);
+      const float m_new = fmaxf(m_ref, m_tile);
+      if (j == 0) {
+        m_ref = m_new;
+      } else {
+        const bool need = (m_new - m_ref) * scale > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), (j - 1) & 1, abortp));
+          if (!ok) { if (lane == 0) record_timeout(p.status, 8); break; }
+          tc_fence_after_sync();
+          float alpha = 1.f;
+          if (need) {
+            alpha = ex2((m_ref - m_new) * scale);
+            m_ref = m_new;
+            l *= alpha;
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + c * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      const float neg_m = -m_ref * scale;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2(fmaf(s[c * 32 + 2 * i], scale, neg_m));
+          const float p1 = ex2(fmaf(s[c * 32 + 2 * i + 1], scale, neg_m));
+          l += p0;
+          l += p1;
+          pk[i] = pack2<kBF16>(p0, p1);
+        }
+        tmem_st16(tS + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars.p_ready[t]));
+    }
+
+    if (ok && n_t > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), (n_t - 1) & 1, abortp));
+      if (!ok && lane == 0) record_timeout(p.status, 9);
+    }
+    if (ok && n_t > 0) {
+      tc_fence_after_sync();
+      const float inv_l = 1.f / l;
+      // Q_t is dead once the last P.V has completed: stage O_t there in the TMA store layout
+      uint8_t* stage = smem_gen + t * kTileBytes;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tO + c * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          v.x = pack2<kBF16>(__uint_as_float(o[g * 8 + 0]) * inv_l, __uint_as_float(o[g * 8 + 1]) * inv_l);
+          v.y = pack2<kBF16>(__uint_as_float(o[g * 8 + 2]) * inv_l, __uint_as_float(o[g * 8 + 3]) * inv_l);
+          v.z = pack2<kBF16>(__uint_as_float(o[g * 8 + 4]) * inv_l, __uint_as_float(o[g * 8 + 5]) * inv_l);
+          v.w = pack2<kBF16>(__uint_as_float(o[g * 8 + 6]) * inv_l, __uint_as_float(o[g * 8 + 7]) * inv_l);
+          const int chunk = c * 4 + g;  // 16-byte chunk of the 256-byte row
+          *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes +
+                                    sw128_offset(r_in_tile, chunk & 7)) = v;
+        }
+      }
+      if (p.lse2 != nullptr && row < p.Sq) {
+        p.lse2[(static_cast<size_t>(b) * p.H + h) * p.Sq + row] = m_ref * scale + log2f(l);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&bars.epi[t]));
+      if (r_in_tile == 0) {
+        if (mbar_wait(smem_u32(&bars.epi[t]), 0, abortp)) {
+          tma_store_4d(&map_o, sQ + t * kTileBytes, 0, h, q0[t], b);
+          tma_store_4d(&map_o, sQ + t * kTileBytes + kHalfBytes, 64, h, q0[t], b);
+          tma_store_commit();
+          tma_store_wait_read();
+        } else {
+          record_timeout(p.status, 10);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, 512);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                            const CUtensorMap& mo, float* lse2, const AttnShape& s,
+                            cudaStream_t stream) {
+  FwdParams p;
+  p.B = s.B;
+  p.H = s.H;
+  p.Sq = s.Sq;
+  p.Skv = s.Skv;
+  p.causal = s.causal;
+  p.diag_off = s.Skv - s.Sq;
+  p.nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
+  p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+  p.lse2 = lse2;
+  p.status = device_status_words();
+  const dim3 grid(static_cast<unsigned>(p.nq_blocks) * s.B * s.H);
+  auto kern = s.bf16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, mo, p);
+  count_launch();
+  return cudaPeekAtLastError();
+}
+
+}  // namespace asuka

@@ -1,0 +1,62 @@
+// Internal launch interface between the C-ABI layer (capi.cu) and the kernel files.
+// All arguments have been validated by the caller.  Each function enqueues on `stream` and
+// returns a cudaError_t from the launch (cudaPeekAtLastError), never synchronising.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace asuka {
+
+// Device-side record of bounded waits that expired: word 0 = count, word 1 = last site id.
+uint32_t* device_status_words();  // device address of a 4-word __device__ array
+void count_launch();
+
+struct AttnShape {
+  int B, H, Sq, Skv;
+  int causal;
+  float softmax_scale;
+  bool bf16;
+};
+
+// q/k/v/out tensor maps: [B,S,H,128] boxes of 64 x 1 x 128 x 1, 128-byte swizzle.
+cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                            const CUtensorMap& mo, float* lse2, const AttnShape& s,
+                            cudaStream_t stream);
+
+struct ScoreArgs {
+  const float* lse2;       // [B,H,Sq]
+  float* score;            // [B,H,Skv]
+  float* score_sq;         // [B,H,Skv] or null
+  const float* exp_rand;   // [B,H,Sq,Skv] or null
+  int64_t er_stride_b, er_stride_h, er_stride_q;  // elements (innermost stride 1)
+  float tau;
+  uint64_t seed;
+  int mode;                // asuka_score_mode
+};
+cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
+                              const AttnShape& s, cudaStream_t stream);
+// Keyformer row statistic: writes lse2' [B,H,Sq] of (s + g) / tau
+cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
+                              float* lse2_out, const AttnShape& s, cudaStream_t stream);
+
+struct SelectArgs {
+  const float* score;     // [B*H, S] rows, contiguous
+  const float* score_sq;  // or null
+  int32_t* idx;           // [B*H, n_out]
+  int rows, S, k_keep, recent, q_len, mode;
+};
+cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream);
+
+struct SimaShape {
+  int B, H, S;
+  bool bf16;
+  bool out_f32;
+};
+size_t sima_workspace_bytes(const SimaShape& s);
+cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                        const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
+                        int64_t out_stride_s, int64_t out_stride_h, void* ws, const SimaShape& s,
+                        cudaStream_t stream);
+
+}  // namespace asuka

@@ -1,0 +1,203 @@
+"""Operator layer: torch tensors in, C-ABI calls, torch tensors out.
+
+Outputs are allocated with torch.empty on the inputs' device and the work is enqueued on torch's
+current stream without synchronising -- the contract of the reference's generated callables
+(lib/Translate/to_triton.cpp:579-609).  Shape/dtype problems raise (as the TensorRT back end's
+closure does, python/asuka/backend/tensorrt/builder.py:104-111); nothing falls back to PyTorch.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import AsukaError  # noqa: F401  (re-exported)
+
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32,
+           torch.int32: _lib.I32}
+
+
+def _desc(t):
+  """asuka_tensor descriptor of a torch tensor (None -> null descriptor)."""
+  d = _lib.Tensor()
+  if t is None:
+    return d
+  if t.dtype not in _DTYPES:
+    raise TypeError(f"unsupported dtype {t.dtype}")
+  if t.dim() > 5:
+    raise ValueError("at most 5 dimensions")
+  d.ptr = t.data_ptr()
+  d.dtype = _DTYPES[t.dtype]
+  d.ndim = t.dim()
+  for i in range(t.dim()):
+    d.shape[i] = t.shape[i]
+    d.stride[i] = t.stride(i)
+  return d
+
+
+def _stream(t):
+  if not t.is_cuda:
+    raise RuntimeError("asuka_b200 kernels run on CUDA tensors only; there is no CPU path")
+  return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _as4d(t):
+  """Accept the 2-D [S, H*D] layout of cases/attn.py as [1, S, H, 128] (same memory)."""
+  if t.dim() == 2:
+    return t.view(1, t.shape[0], t.shape[1] // 128, 128)
+  return t
+
+
+def _same_device(*ts):
+  dev = ts[0].device
+  for t in ts:
+    if t is not None and t.device != dev:
+      raise RuntimeError("all tensors must be on the same device")
+
+
+def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None):
+  """out = softmax(q k^T * scale (+ causal mask)) v.  q: [B,Sq,H,128]; k, v: [B,Skv,H,128]."""
+  lib = _lib.load()
+  q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
+  _same_device(q4, k4, v4)
+  with torch.cuda.device(q4.device):
+    if out is None:
+      out = torch.empty(q4.shape, dtype=q4.dtype, device=q4.device)
+    lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32,
+                      device=q4.device) if return_lse else None
+    p = _lib.AttnParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(lse),
+                        float(softmax_scale), int(bool(causal)))
+    _lib.check("asuka_b200_attn_fwd", lib.asuka_b200_attn_fwd(ctypes.byref(p), _stream(q4)))
+  out = out.view(q.shape) if q.dim() == 2 else out
+  return (out, lse) if return_lse else out
+
+
+def col_scores(q, k, lse, mode=_lib.SCORE_SUM, causal=True, softmax_scale=0.0, exp_rand=None,
+               tau=1.0, seed=0):
+  """Per-key sums over the query rows of the attention probabilities: [B,H,Skv] f32
+  (and the sum of squares in mode SCORE_SUM_SQ)."""
+  lib = _lib.load()
+  q4, k4 = _as4d(q), _as4d(k)
+  _same_device(q4, k4, lse, exp_rand)
+  B, Skv, H = k4.shape[0], k4.shape[1], k4.shape[2]
+  with torch.cuda.device(q4.device):
+    score = torch.empty((B, H, Skv), dtype=torch.float32, device=q4.device)
+    score_sq = torch.empty_like(score) if mode == _lib.SCORE_SUM_SQ else None
+    p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _desc(score), _desc(score_sq),
+                         _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
+                         int(bool(causal)), int(mode))
+    _lib.check("asuka_b200_col_scores", lib.asuka_b200_col_scores(ctypes.byref(p), _stream(q4)))
+  return (score, score_sq) if score_sq is not None else score
+
+
+def keyformer_rowstat(q, k, causal=True, softmax_scale=0.0, exp_rand=None, tau=1.5, seed=0):
+  """Base-2 log-sum-exp per query row of the perturbed logits (s + g) / tau: [B,H,Sq] f32."""
+  lib = _lib.load()
+  q4, k4 = _as4d(q), _as4d(k)
+  _same_device(q4, k4, exp_rand)
+  with torch.cuda.device(q4.device):
+    lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32, device=q4.device)
+    p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _lib.Tensor(), _lib.Tensor(),
+                         _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
+                         int(bool(causal)), _lib.SCORE_PERTURBED)
+    _lib.check("asuka_b200_keyformer_rowstat",
+               lib.asuka_b200_keyformer_rowstat(ctypes.byref(p), _stream(q4)))
+  return lse
+
+
+def select_topk(score, k_keep, mode=_lib.SELECT_TOPK, recent=0, score_sq=None, q_len=0):
+  """Kept key indices, ascending int32 [B,H,k_keep(+recent)]."""
+  lib = _lib.load()
+  _same_device(score, score_sq)
+  B, H, _ = score.shape
+  n_out = k_keep + (recent if mode == _lib.SELECT_TOPK_RECENT else 0)
+  with torch.cuda.device(score.device):
+    idx = torch.empty((B, H, n_out), dtype=torch.int32, device=score.device)
+    p = _lib.SelectParams(_desc(score), _desc(score_sq), _desc(idx), int(k_keep), int(recent),
+                          int(q_len), int(mode))
+    _lib.check("asuka_b200_select_topk", lib.asuka_b200_select_topk(ctypes.byref(p), _stream(score)))
+  return idx
+
+
+def sima_fwd(q, k, v, out_dtype=None):
+  """SimA: out = L1norm_seq(q) (L1norm_seq(k)^T v), [B,S,H,128]."""
+  lib = _lib.load()
+  q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
+  _same_device(q4, k4, v4)
+  with torch.cuda.device(q4.device):
+    out = torch.empty(q4.shape, dtype=out_dtype or q4.dtype, device=q4.device)
+    p = _lib.SimaParams(_desc(q4), _desc(k4), _desc(v4), _desc(out))
+    nbytes = ctypes.c_size_t(0)
+    _lib.check("asuka_b200_sima_workspace_bytes",
+               lib.asuka_b200_sima_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)))
+    ws = torch.empty((max(nbytes.value, 16),), dtype=torch.uint8, device=q4.device)
+    _lib.check("asuka_b200_sima_fwd",
+               lib.asuka_b200_sima_fwd(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()),
+                                       ctypes.c_size_t(ws.numel()), _stream(q4)))
+  return out.view(q.shape) if q.dim() == 2 else out
+
+
+def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None, tau=1.0, seed=0,
+          k_keep=0, recent=0, n_idx=0, workspace=None, out=None, score=None, score_sq=None, idx=None):
+  lib = _lib.load()
+  q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
+  _same_device(q4, k4, v4, exp_rand)
+  B, Skv, H = k4.shape[0], k4.shape[1], k4.shape[2]
+  dev = q4.device
+  with torch.cuda.device(dev):
+    if out is None:
+      out = torch.empty(q4.shape, dtype=q4.dtype, device=dev)
+    if score is None:
+      score = torch.empty((B, H, Skv), dtype=torch.float32, device=dev)
+    if want_sq and score_sq is None:
+      score_sq = torch.empty_like(score)
+    if n_idx > 0 and idx is None:
+      idx = torch.empty((B, H, n_idx), dtype=torch.int32, device=dev)
+    p = _lib.CaseParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(score),
+                        _desc(score_sq), _desc(exp_rand), _desc(idx), float(softmax_scale),
+                        float(tau), int(seed), int(bool(causal)), int(k_keep), int(recent))
+    if workspace is None:
+      nbytes = ctypes.c_size_t(0)
+      _lib.check("asuka_b200_case_workspace_bytes",
+                 lib.asuka_b200_case_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)))
+      workspace = torch.empty((max(nbytes.value, 16),), dtype=torch.uint8, device=dev)
+    _lib.check(fn_name, getattr(lib, fn_name)(ctypes.byref(p), ctypes.c_void_p(workspace.data_ptr()),
+                                              ctypes.c_size_t(workspace.numel()), _stream(q4)))
+  out = out.view(q.shape) if q.dim() == 2 else out
+  return out, score, score_sq, idx
+
+
+def h2o(q, k, v, causal=True, softmax_scale=0.0, k_keep=0, recent=0, **buffers):
+  """(out, h2o_score[, idx]) -- cases/kernels/h2o.py:18-38 plus the optional keep set."""
+  n_idx = k_keep + recent if k_keep > 0 else 0
+  out, score, _, idx = _case("asuka_b200_h2o", q, k, v, causal, softmax_scale, k_keep=k_keep,
+                             recent=recent, n_idx=n_idx, **buffers)
+  return (out, score, idx) if n_idx else (out, score)
+
+
+def roco(q, k, v, causal=True, softmax_scale=0.0, k_keep=0, **buffers):
+  """(out, roco_score, roco_sq_score[, idx]) -- cases/kernels/roco.py:18-48."""
+  out, score, sq, idx = _case("asuka_b200_roco", q, k, v, causal, softmax_scale, want_sq=True,
+                              k_keep=k_keep, n_idx=k_keep, **buffers)
+  return (out, score, sq, idx) if k_keep else (out, score, sq)
+
+
+def keyformer(q, k, v, exp_rand=None, tau=1.5, seed=0, causal=True, softmax_scale=0.0, k_keep=0,
+              **buffers):
+  """(out, kf_score[, idx]) -- cases/kernels/kf.py:19-42; exp_rand=None uses the seeded noise."""
+  out, score, _, idx = _case("asuka_b200_keyformer", q, k, v, causal, softmax_scale,
+                             exp_rand=exp_rand, tau=tau, seed=seed, k_keep=k_keep, n_idx=k_keep,
+                             **buffers)
+  return (out, score, idx) if k_keep else (out, score)
+
+
+def device_status():
+  """(count, last_site) of expired device-side waits since the last read; raises if non-zero."""
+  lib = _lib.load()
+  w = (ctypes.c_uint32 * 2)()
+  st = lib.asuka_b200_device_status(w)
+  _lib.check("asuka_b200_device_status", st)
+  return int(w[0]), int(w[1])
+
+
+def launch_count():
+  return int(_lib.load().asuka_b200_launch_count())

@@ -1,0 +1,188 @@
+/*
+ * asuka_b200 -- C ABI of the hand-written sm_100a kernel library that stands in for the kernels
+ * the FlashTensor/Asuka compiler generates for its fused-attention programs.
+ *
+ * What each entry point replaces in the reference:
+ *   The reference emits, per fused kernel, a Python function
+ *       def <KernelName>(arg0: torch.Tensor, ...) -> Tensor | Tuple[Tensor, ...]
+ *   that allocates its outputs and launches one generated Triton kernel on the current stream
+ *   (lib/Translate/to_triton.cpp:529-638).  The functions below are the bodies of those
+ *   callables for the attention programs of cases/kernels/{attn,h2o,kf,roco}.py and
+ *   bench/sima.mlir: plain pointers and sizes in, work enqueued on the given stream, integer
+ *   status out.  The Python package `flashtensor_b200` wraps them back into the reference's
+ *   per-case callables and its back-end plug-in interface (python/asuka/backend/builder.py:7-14).
+ *
+ * Conventions
+ *   - Every function returns ASUKA_OK (0) or a negative asuka_status; nothing throws or aborts.
+ *   - Arguments are validated on the host before anything is launched.
+ *   - The library allocates nothing and keeps no pointer after a call returns.  The caller owns
+ *     inputs, outputs and workspaces.
+ *   - Work is enqueued on `stream` of the CURRENT device; calls do not synchronise.
+ *   - Tensors are described by asuka_tensor: strides are in ELEMENTS; the innermost (head_dim)
+ *     stride must be 1 and every other stride a multiple of 8 elements (16 bytes); base
+ *     pointers must be 16-byte aligned.
+ *   - q, k, v, out use the reference's [B, S, H, D] layout (cases/kernels/attn.py:37-39) with
+ *     D = 128; the 2-D [S, H*D] layout of cases/attn.py is the same memory with B = 1.
+ *   - Per-key scores use the reference's [B, H, S_kv] fp32 layout (cases/kernels/h2o.py:38).
+ */
+#ifndef ASUKA_B200_H_
+#define ASUKA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  ASUKA_OK = 0,
+  ASUKA_ERR_NULL_POINTER = -1,
+  ASUKA_ERR_BAD_DTYPE = -2,
+  ASUKA_ERR_BAD_SHAPE = -3,
+  ASUKA_ERR_BAD_STRIDE = -4,
+  ASUKA_ERR_MISALIGNED = -5,
+  ASUKA_ERR_WORKSPACE_TOO_SMALL = -6,
+  ASUKA_ERR_UNSUPPORTED_ARCH = -7,
+  ASUKA_ERR_CUDA = -8,
+  ASUKA_ERR_DEVICE_TIMEOUT = -9,
+  ASUKA_ERR_BAD_ARGUMENT = -10,
+  ASUKA_ERR_TOO_LARGE = -11
+} asuka_status;
+
+typedef enum { ASUKA_F16 = 0, ASUKA_BF16 = 1, ASUKA_F32 = 2, ASUKA_I32 = 3 } asuka_dtype;
+
+typedef struct {
+  void* ptr;
+  int32_t dtype; /* asuka_dtype */
+  int32_t ndim;
+  int64_t shape[5];
+  int64_t stride[5]; /* in elements */
+} asuka_tensor;
+
+/* Opaque to C callers: a CUDA stream handle (cudaStream_t). */
+typedef void* asuka_stream;
+
+/* ---- attention forward: replaces the generated kernel for Attn.forward
+ *      (cases/kernels/attn.py:18-34; unmasked form cases/attn.py:44-63). ---- */
+typedef struct {
+  asuka_tensor q;   /* [B, Sq,  H, 128] f16 | bf16 */
+  asuka_tensor k;   /* [B, Skv, H, 128] same dtype */
+  asuka_tensor v;   /* [B, Skv, H, 128] same dtype */
+  asuka_tensor out; /* [B, Sq,  H, 128] same dtype */
+  asuka_tensor lse; /* optional (ptr may be NULL): [B, H, Sq] f32, contiguous.  Receives the
+                       base-2 log-sum-exp of the scaled logits of every query row; it is the
+                       per-row statistic the column-score pass needs. */
+  float softmax_scale; /* <= 0 selects 1/sqrt(128) */
+  int32_t causal;      /* 1: key j is visible to query i iff j <= i + (Skv - Sq)
+                          (torch.triu(-inf, diagonal=kv_len-q_len+1), cases/kernels/attn.py:22-23) */
+} asuka_attn_params;
+
+int asuka_b200_attn_fwd(const asuka_attn_params* p, asuka_stream stream);
+
+/* ---- per-key column reductions of the attention probabilities: replaces the generated
+ *      column kernel for h2o_score (cases/kernels/h2o.py:35-36), roco_score / roco_sq_score
+ *      (cases/kernels/roco.py:42-46) and kf_score (cases/kernels/kf.py:36-40). ---- */
+typedef enum {
+  ASUKA_SCORE_SUM = 0,       /* sum_i p_ij                          (H2O)      */
+  ASUKA_SCORE_SUM_SQ = 1,    /* sum_i p_ij and sum_i p_ij^2         (RoCo)     */
+  ASUKA_SCORE_PERTURBED = 2  /* sum_i softmax_j((s_ij + g_ij)/tau)  (Keyformer) */
+} asuka_score_mode;
+
+typedef struct {
+  asuka_tensor q;        /* [B, Sq,  H, 128] */
+  asuka_tensor k;        /* [B, Skv, H, 128] */
+  asuka_tensor lse;      /* [B, H, Sq] f32: row statistic from asuka_b200_attn_fwd (modes 0, 1) or
+                            from asuka_b200_keyformer_rowstat (mode 2) */
+  asuka_tensor score;    /* [B, H, Skv] f32 out */
+  asuka_tensor score_sq; /* [B, H, Skv] f32 out, mode ASUKA_SCORE_SUM_SQ only */
+  asuka_tensor exp_rand; /* mode 2: [B, H, Sq, Skv] f32 > 0, noise g = -log(exp_rand)
+                            (cases/kernels/kf.py:36-37); ptr NULL selects the seeded generator */
+  float softmax_scale;
+  float tau;             /* mode 2 temperature (cases/kernels/kf.py:8) */
+  uint64_t seed;         /* mode 2 with exp_rand.ptr == NULL */
+  int32_t causal;
+  int32_t mode;          /* asuka_score_mode */
+} asuka_score_params;
+
+int asuka_b200_col_scores(const asuka_score_params* p, asuka_stream stream);
+
+/* Row statistic of Keyformer's perturbed softmax (base-2 log-sum-exp of (s + g)/tau per query
+ * row), the input `lse` of asuka_b200_col_scores in mode ASUKA_SCORE_PERTURBED.  Uses q, k,
+ * exp_rand | seed, tau, softmax_scale, causal of `p` and writes p->lse. */
+int asuka_b200_keyformer_rowstat(const asuka_score_params* p, asuka_stream stream);
+
+/* ---- heavy-hitter selection.  The reference has no counterpart (it stops at the scores);
+ *      the rules are the ones the benchmark configuration states. ---- */
+typedef enum {
+  ASUKA_SELECT_TOPK = 0,        /* k largest keys, ties -> lower index                       */
+  ASUKA_SELECT_TOPK_RECENT = 1, /* k largest among [0, S-recent) plus the last `recent`      */
+  ASUKA_SELECT_ROCO = 2         /* k largest mean = sum/n_j, ties -> larger std, lower index */
+} asuka_select_mode;
+
+typedef struct {
+  asuka_tensor score;    /* [B, H, S] f32, values >= 0 */
+  asuka_tensor score_sq; /* [B, H, S] f32, mode ROCO only */
+  asuka_tensor idx;      /* [B, H, k_keep (+ recent)] i32 out, ascending */
+  int32_t k_keep;
+  int32_t recent; /* mode TOPK_RECENT */
+  int32_t q_len;  /* mode ROCO: n_j = q_len - max(0, j - (S - q_len)) */
+  int32_t mode;   /* asuka_select_mode */
+} asuka_select_params;
+
+int asuka_b200_select_topk(const asuka_select_params* p, asuka_stream stream);
+
+/* ---- SimA softmax-free attention: replaces the generated kernels for bench/sima.mlir:13-17
+ *      (L1 normalisation as lib/Dialect/Asuka/Transforms/LowerComplexReduce.cpp:44-69). ---- */
+typedef struct {
+  asuka_tensor q;   /* [B, S, H, 128] f16 | bf16 */
+  asuka_tensor k;
+  asuka_tensor v;
+  asuka_tensor out; /* [B, S, H, 128] same dtype, or f32 */
+} asuka_sima_params;
+
+/* Bytes of device workspace asuka_b200_sima_fwd needs for these shapes (pure host function). */
+int asuka_b200_sima_workspace_bytes(const asuka_sima_params* p, size_t* bytes);
+int asuka_b200_sima_fwd(const asuka_sima_params* p, void* workspace, size_t workspace_bytes,
+                        asuka_stream stream);
+
+/* ---- fused cases: forward + column scores (+ selection) enqueued back to back on one stream.
+ *      `workspace` holds the row statistic between the two kernels: B*H*Sq floats. ---- */
+typedef struct {
+  asuka_tensor q, k, v, out;
+  asuka_tensor score;    /* h2o_score | kf_score | roco_score, [B, H, Skv] f32 */
+  asuka_tensor score_sq; /* RoCo only */
+  asuka_tensor exp_rand; /* Keyformer only; ptr NULL selects the seeded generator */
+  asuka_tensor idx;      /* optional (ptr may be NULL): kept indices, i32 */
+  float softmax_scale;
+  float tau;
+  uint64_t seed;
+  int32_t causal;
+  int32_t k_keep;
+  int32_t recent;
+} asuka_case_params;
+
+int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes);
+/* H2O.forward, cases/kernels/h2o.py:18-38 (+ selection) */
+int asuka_b200_h2o(const asuka_case_params* p, void* workspace, size_t workspace_bytes,
+                   asuka_stream stream);
+/* RoCo.forward, cases/kernels/roco.py:18-48 (+ selection) */
+int asuka_b200_roco(const asuka_case_params* p, void* workspace, size_t workspace_bytes,
+                    asuka_stream stream);
+/* KeyFormer.forward, cases/kernels/kf.py:19-42 (+ selection) */
+int asuka_b200_keyformer(const asuka_case_params* p, void* workspace, size_t workspace_bytes,
+                         asuka_stream stream);
+
+/* ---- library services ---- */
+int asuka_b200_version(void);
+const char* asuka_b200_strerror(int status);
+/* Kernels bound every wait; one that gives up records it in a device-side word.  This reads the
+ * word (synchronising the current device) and clears it: 0 = no time-out since the last read. */
+int asuka_b200_device_status(uint32_t* out);
+/* Number of kernels this library has launched in this process (for launch accounting). */
+uint64_t asuka_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASUKA_B200_H_ */
