@@ -138,6 +138,205 @@ int attn_fwd_impl(const asuka_attn_params* p, float* lse_override, cudaStream_t 
   return map_cuda(launch_attn_fwd(mq, mk, mv, mo, lse, c.s, stream));
 }
 
+
+int check_er(const asuka_tensor& er, const AttnShape& s) {
+  if (er.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (er.dtype != ASUKA_F32) return ASUKA_ERR_BAD_DTYPE;
+  if (er.ndim != 4) return ASUKA_ERR_BAD_SHAPE;
+  if (er.shape[0] != s.B || er.shape[1] != s.H || er.shape[2] != s.Sq || er.shape[3] != s.Skv)
+    return ASUKA_ERR_BAD_SHAPE;
+  if (er.stride[3] != 1 || er.stride[0] < 0 || er.stride[1] < 0 || er.stride[2] < 0)
+    return ASUKA_ERR_BAD_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(er.ptr) & 3u) != 0) return ASUKA_ERR_MISALIGNED;
+  return ASUKA_OK;
+}
+
+// validates a score request and fills the launch arguments; `lse` is the row statistic to read
+int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a) {
+  if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
+  int r;
+  if ((r = check_qk(p->q, p->k, p->softmax_scale, p->causal, c)) != ASUKA_OK) return r;
+  if (p->mode != ASUKA_SCORE_SUM && p->mode != ASUKA_SCORE_SUM_SQ && p->mode != ASUKA_SCORE_PERTURBED)
+    return ASUKA_ERR_BAD_ARGUMENT;
+  const int64_t lshape[3] = {c->s.B, c->s.H, c->s.Sq};
+  const int64_t sshape[3] = {c->s.B, c->s.H, c->s.Skv};
+  if ((r = check_dense(p->lse, ASUKA_F32, 3, lshape)) != ASUKA_OK) return r;
+  std::memset(a, 0, sizeof(*a));
+  a->mode = p->mode;
+  a->lse2 = static_cast<const float*>(p->lse.ptr);
+  a->tau = 1.f;
+  if (!rowstat) {
+    if ((r = check_dense(p->score, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
+    a->score = static_cast<float*>(p->score.ptr);
+    if (p->mode == ASUKA_SCORE_SUM_SQ) {
+      if ((r = check_dense(p->score_sq, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
+      a->score_sq = static_cast<float*>(p->score_sq.ptr);
+    }
+  }
+  if (p->mode == ASUKA_SCORE_PERTURBED) {
+    if (!(p->tau > 0.f) || std::isinf(p->tau)) return ASUKA_ERR_BAD_ARGUMENT;
+    a->tau = p->tau;
+    a->seed = p->seed;
+    if (p->exp_rand.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;  // seeded generator: not built yet
+    if ((r = check_er(p->exp_rand, c->s)) != ASUKA_OK) return r;
+    a->exp_rand = static_cast<const float*>(p->exp_rand.ptr);
+    a->er_stride_b = p->exp_rand.stride[0];
+    a->er_stride_h = p->exp_rand.stride[1];
+    a->er_stride_q = p->exp_rand.stride[2];
+  } else if (rowstat) {
+    return ASUKA_ERR_BAD_ARGUMENT;
+  }
+  return check_arch();
+}
+
+int col_scores_impl(const asuka_score_params* p, cudaStream_t stream) {
+  QKV c;
+  ScoreArgs a;
+  int r = prep_scores(p, false, &c, &a);
+  if (r != ASUKA_OK) return r;
+  CUtensorMap mq, mk;
+  if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k))) return r;
+  return map_cuda(launch_col_scores(mq, mk, a, c.s, stream));
+}
+
+int kf_rowstat_impl(const asuka_score_params* p, cudaStream_t stream) {
+  QKV c;
+  ScoreArgs a;
+  int r = prep_scores(p, true, &c, &a);
+  if (r != ASUKA_OK) return r;
+  CUtensorMap mq, mk;
+  if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k))) return r;
+  return map_cuda(launch_kf_rowstat(mq, mk, a, static_cast<float*>(p->lse.ptr), c.s, stream));
+}
+
+constexpr int kSelectMaxS32 = 32768;  // 4-byte keys in shared memory
+constexpr int kSelectMaxS64 = 16384;  // 8-byte keys (RoCo)
+
+int select_impl(const asuka_select_params* p, cudaStream_t stream) {
+  if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (p->score.ptr == nullptr || p->idx.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (p->mode != ASUKA_SELECT_TOPK && p->mode != ASUKA_SELECT_TOPK_RECENT && p->mode != ASUKA_SELECT_ROCO)
+    return ASUKA_ERR_BAD_ARGUMENT;
+  if (p->score.ndim != 3) return ASUKA_ERR_BAD_SHAPE;
+  const int64_t B = p->score.shape[0], H = p->score.shape[1], S = p->score.shape[2];
+  if (B <= 0 || H <= 0 || S <= 0) return ASUKA_ERR_BAD_SHAPE;
+  const int64_t sshape[3] = {B, H, S};
+  int r;
+  if ((r = check_dense(p->score, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
+  const bool roco = p->mode == ASUKA_SELECT_ROCO;
+  if (S > (roco ? kSelectMaxS64 : kSelectMaxS32) || B * H > 0x7fffffff) return ASUKA_ERR_TOO_LARGE;
+  const int recent = p->mode == ASUKA_SELECT_TOPK_RECENT ? p->recent : 0;
+  if (recent < 0 || recent > S) return ASUKA_ERR_BAD_ARGUMENT;
+  if (p->k_keep < 1 || p->k_keep > S - recent) return ASUKA_ERR_BAD_ARGUMENT;
+  if (roco) {
+    if ((r = check_dense(p->score_sq, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
+    if (p->q_len < 1 || p->q_len > S) return ASUKA_ERR_BAD_ARGUMENT;
+  }
+  const int64_t ishape[3] = {B, H, p->k_keep + recent};
+  if ((r = check_dense(p->idx, ASUKA_I32, 3, ishape)) != ASUKA_OK) return r;
+  if ((r = check_arch()) != ASUKA_OK) return r;
+  SelectArgs a;
+  a.score = static_cast<const float*>(p->score.ptr);
+  a.score_sq = roco ? static_cast<const float*>(p->score_sq.ptr) : nullptr;
+  a.idx = static_cast<int32_t*>(p->idx.ptr);
+  a.rows = static_cast<int>(B * H);
+  a.S = static_cast<int>(S);
+  a.k_keep = p->k_keep;
+  a.recent = recent;
+  a.q_len = p->q_len;
+  a.mode = p->mode;
+  return map_cuda(launch_select(a, stream));
+}
+
+// forward + column scores (+ selection) on one stream; the row statistic lives in `ws`
+enum CaseKind { CASE_H2O, CASE_ROCO, CASE_KF };
+
+size_t case_ws_bytes(const asuka_case_params* p) {
+  const size_t n = static_cast<size_t>(p->q.shape[0]) * p->q.shape[2] * p->q.shape[1];
+  return ((n * sizeof(float) + 255) / 256) * 256 * 2;  // unperturbed + perturbed row statistics
+}
+
+int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_bytes,
+              cudaStream_t stream) {
+  if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (p->q.ptr == nullptr || p->q.ndim != 4) return p->q.ptr ? ASUKA_ERR_BAD_SHAPE : ASUKA_ERR_NULL_POINTER;
+  for (int i = 0; i < 3; ++i)
+    if (p->q.shape[i] <= 0) return ASUKA_ERR_BAD_SHAPE;
+  if (ws == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if ((reinterpret_cast<uintptr_t>(ws) & 15u) != 0) return ASUKA_ERR_MISALIGNED;
+  if (ws_bytes < case_ws_bytes(p)) return ASUKA_ERR_WORKSPACE_TOO_SMALL;
+  const int64_t B = p->q.shape[0], Sq = p->q.shape[1], H = p->q.shape[2];
+  float* lse = static_cast<float*>(ws);
+  float* lse_kf = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + case_ws_bytes(p) / 2);
+
+  // validate everything before the first launch
+  asuka_tensor lse_t;
+  std::memset(&lse_t, 0, sizeof(lse_t));
+  lse_t.ptr = lse;
+  lse_t.dtype = ASUKA_F32;
+  lse_t.ndim = 3;
+  lse_t.shape[0] = B; lse_t.shape[1] = H; lse_t.shape[2] = Sq;
+  lse_t.stride[0] = H * Sq; lse_t.stride[1] = Sq; lse_t.stride[2] = 1;
+
+  asuka_attn_params fp;
+  std::memset(&fp, 0, sizeof(fp));
+  fp.q = p->q; fp.k = p->k; fp.v = p->v; fp.out = p->out;
+  fp.lse = lse_t;
+  fp.softmax_scale = p->softmax_scale;
+  fp.causal = p->causal;
+
+  asuka_score_params sp;
+  std::memset(&sp, 0, sizeof(sp));
+  sp.q = p->q; sp.k = p->k; sp.lse = lse_t; sp.score = p->score; sp.score_sq = p->score_sq;
+  sp.exp_rand = p->exp_rand;
+  sp.softmax_scale = p->softmax_scale;
+  sp.tau = p->tau;
+  sp.seed = p->seed;
+  sp.causal = p->causal;
+  sp.mode = kind == CASE_H2O ? ASUKA_SCORE_SUM : kind == CASE_ROCO ? ASUKA_SCORE_SUM_SQ : ASUKA_SCORE_PERTURBED;
+  if (kind == CASE_KF) sp.lse.ptr = lse_kf;
+
+  asuka_select_params lp;
+  std::memset(&lp, 0, sizeof(lp));
+  const bool want_idx = p->idx.ptr != nullptr;
+  if (want_idx) {
+    lp.score = p->score; lp.score_sq = p->score_sq; lp.idx = p->idx;
+    lp.k_keep = p->k_keep;
+    lp.recent = p->recent;
+    lp.q_len = static_cast<int32_t>(Sq);
+    lp.mode = kind == CASE_H2O ? ASUKA_SELECT_TOPK_RECENT : kind == CASE_ROCO ? ASUKA_SELECT_ROCO : ASUKA_SELECT_TOPK;
+  }
+
+  // dry validation pass: the three impls validate before launching, so run their checks first
+  {
+    QKV c; ScoreArgs a;
+    int r = prep_scores(&sp, false, &c, &a);
+    if (r != ASUKA_OK) return r;
+    if ((r = check_bshd(p->v, c.dtype)) != ASUKA_OK) return r;
+    if ((r = check_bshd(p->out, c.dtype)) != ASUKA_OK) return r;
+    for (int i = 0; i < 4; ++i)
+      if (p->v.shape[i] != p->k.shape[i] || p->out.shape[i] != p->q.shape[i]) return ASUKA_ERR_BAD_SHAPE;
+    if (want_idx) {
+      const int64_t S = p->score.shape[2];
+      const bool roco = kind == CASE_ROCO;
+      const int recent = kind == CASE_H2O ? p->recent : 0;
+      if (S > (roco ? kSelectMaxS64 : kSelectMaxS32)) return ASUKA_ERR_TOO_LARGE;
+      if (recent < 0 || recent > S || p->k_keep < 1 || p->k_keep > S - recent) return ASUKA_ERR_BAD_ARGUMENT;
+      const int64_t ishape[3] = {B, H, p->k_keep + recent};
+      if ((r = check_dense(p->idx, ASUKA_I32, 3, ishape)) != ASUKA_OK) return r;
+    }
+  }
+
+  int r = attn_fwd_impl(&fp, nullptr, stream);
+  if (r != ASUKA_OK) return r;
+  if (kind == CASE_KF) {
+    if ((r = kf_rowstat_impl(&sp, stream)) != ASUKA_OK) return r;
+  }
+  if ((r = col_scores_impl(&sp, stream)) != ASUKA_OK) return r;
+  if (want_idx) r = select_impl(&lp, stream);
+  return r;
+}
+
 }  // namespace
 }  // namespace asuka
 
@@ -184,6 +383,37 @@ int asuka_b200_device_status(uint32_t* out) {
 
 int asuka_b200_attn_fwd(const asuka_attn_params* p, asuka_stream stream) {
   return attn_fwd_impl(p, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int asuka_b200_col_scores(const asuka_score_params* p, asuka_stream stream) {
+  return col_scores_impl(p, static_cast<cudaStream_t>(stream));
+}
+
+int asuka_b200_keyformer_rowstat(const asuka_score_params* p, asuka_stream stream) {
+  return kf_rowstat_impl(p, static_cast<cudaStream_t>(stream));
+}
+
+int asuka_b200_select_topk(const asuka_select_params* p, asuka_stream stream) {
+  return select_impl(p, static_cast<cudaStream_t>(stream));
+}
+
+int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes) {
+  if (p == nullptr || bytes == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (p->q.ndim != 4) return ASUKA_ERR_BAD_SHAPE;
+  for (int i = 0; i < 3; ++i)
+    if (p->q.shape[i] <= 0) return ASUKA_ERR_BAD_SHAPE;
+  *bytes = case_ws_bytes(p);
+  return ASUKA_OK;
+}
+
+int asuka_b200_h2o(const asuka_case_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
+  return case_impl(p, CASE_H2O, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+int asuka_b200_roco(const asuka_case_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
+  return case_impl(p, CASE_ROCO, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+int asuka_b200_keyformer(const asuka_case_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
+  return case_impl(p, CASE_KF, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,0 +1,516 @@
+// Per-key column reductions of the attention probabilities for sm_100a.
+//
+// Replaces the column kernel the Asuka pipeline generates beside the forward kernel for
+//   h2o_score   = probs.sum(dim=2)                       (cases/kernels/h2o.py:35-36)
+//   roco_score, roco_sq_score = sum p, sum p^2           (cases/kernels/roco.py:42-46)
+//   kf_score    = softmax((scores + g)/tau).sum(dim=2)   (cases/kernels/kf.py:36-40)
+// It needs every row's softmax denominator first, so it recomputes S from Q and K and reads the
+// per-row base-2 log-sum-exp written by the forward kernel (or by the Keyformer row pass below).
+//
+// Orientation is transposed: S^T = K Q^T, so TMEM lane = key and one thread owns one key.  A
+// key's sum over all query rows is then a serial f32 sum in one thread, in a fixed order: no
+// cross-thread or cross-CTA reduction exists, and results are bitwise reproducible.
+//   warp 0      producer: two resident K tiles (256 keys), Q tiles + their row statistics in a ring
+//   warp 1      tcgen05.mma issuer: S^T_t[buf] = K_t Q_i^T into one of two TMEM buffers per key tile
+//   warps 4-7   keys   0..127 of the block: exp2, mask, accumulate
+//   warps 8-11  keys 128..255
+//
+// The Keyformer row pass (kf_rowstat) is the row-oriented counterpart: S = Q K^T, one thread per
+// query row, online max/sum of the perturbed logits, nothing else.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../../include/asuka_b200.h"
+#include "kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace asuka {
+using namespace sm100;
+
+namespace {
+
+constexpr int kTile = 128;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;
+constexpr uint32_t kHalfBytes = kTileBytes / 2;
+constexpr int kQStages = 4;
+constexpr int kThreads = 384;
+constexpr uint32_t kSmemBytes = (2 + kQStages) * kTileBytes + 1024;
+
+struct ColParams {
+  int B, H, Sq, Skv;
+  int causal, diag_off;
+  int nq_tiles;
+  float scale_log2;   // softmax_scale * log2(e) (perturbed mode: additionally / tau)
+  float inv_tau;
+  const float* lse2;  // [B,H,Sq]
+  float* score;       // [B,H,Skv]
+  float* score_sq;
+  const float* exp_rand;
+  int64_t er_sb, er_sh, er_sq;
+  uint32_t* status;
+};
+
+struct ColBars {
+  uint64_t k_full;
+  uint64_t q_full[kQStages], q_empty[kQStages];
+  uint64_t s_full[2][2], s_empty[2][2];
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void record_timeout(uint32_t* status, uint32_t site) {
+  atomicAdd(&status[0], 1u);
+  status[1] = site;
+}
+
+// kMode: 0 sum, 1 sum + sum of squares, 2 perturbed (noise operand)
+template <bool kBF16, int kMode>
+__global__ void __launch_bounds__(kThreads, 1)
+col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const ColParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) ColBars bars;
+  __shared__ __align__(16) float lse_s[kQStages][kTile];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_s;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sK = smem_base;                    // 2 tiles
+  const uint32_t sQ = smem_base + 2 * kTileBytes;   // kQStages tiles
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  volatile uint32_t* abortp = &abort_s;
+
+  const int bh_count = p.B * p.H;
+  const int kvb = static_cast<int>(blockIdx.x) / bh_count;  // low key blocks are the long ones
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int b = bh / p.H, h = bh % p.H;
+  const int kv0[2] = {kvb * 2 * kTile, kvb * 2 * kTile + kTile};
+  const bool active[2] = {kv0[0] < p.Skv, kv0[1] < p.Skv};
+  // first query tile that can see the first key of each key tile
+  int i_start[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) i_start[t] = p.causal ? max(0, kv0[t] - p.diag_off) / kTile : 0;
+  const int i_begin = i_start[0];
+  const int n_active = (active[0] ? 1 : 0) + (active[1] ? 1 : 0);
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&bars.k_full), 1);
+    for (int i = 0; i < kQStages; ++i) {
+      mbar_init(smem_u32(&bars.q_full[i]), 1);
+      mbar_init(smem_u32(&bars.q_empty[i]), 1 + 4 * n_active);
+    }
+    for (int t = 0; t < 2; ++t)
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&bars.s_full[t][i]), 1);
+        mbar_init(smem_u32(&bars.s_empty[t][i]), 128);
+      }
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (whole warp)
+    if (lane == 0) {
+      const uint32_t bar = smem_u32(&bars.k_full);
+      mbar_expect_tx(bar, kTileBytes * n_active);
+      for (int t = 0; t < 2; ++t) {
+        if (active[t]) {
+          tma_load_4d(sK + t * kTileBytes, &map_k, bar, 0, h, kv0[t], b);
+          tma_load_4d(sK + t * kTileBytes + kHalfBytes, &map_k, bar, 64, h, kv0[t], b);
+        }
+      }
+    }
+    const float* lse_row = p.lse2 + (static_cast<size_t>(b) * p.H + h) * p.Sq;
+    bool ok = true;
+    for (int i = i_begin; i < p.nq_tiles; ++i) {
+      const int c = i - i_begin;
+      const int st = c % kQStages;
+      const uint32_t use = static_cast<uint32_t>(c / kQStages);
+      if (use > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_empty[st]), (use - 1) & 1, abortp));
+        if (!ok) { if (lane == 0) record_timeout(p.status, 21); break; }
+      }
+      // row statistics of this query tile; rows past the end get +inf so that exp2 gives 0
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int qi = i * kTile + r * 32 + lane;
+        lse_s[st][r * 32 + lane] = qi < p.Sq ? __ldg(lse_row + qi) : INFINITY;
+      }
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t bar = smem_u32(&bars.q_full[st]);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sQ + st * kTileBytes, &map_q, bar, 0, h, i * kTile, b);
+        tma_load_4d(sQ + st * kTileBytes + kHalfBytes, &map_q, bar, 64, h, i * kTile, b);
+      }
+    }
+    if (!ok && lane == 0) {
+      volatile uint32_t none = 0;
+      mbar_wait(smem_u32(&bars.k_full), 0, &none);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+      constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
+      bool ok = mbar_wait(smem_u32(&bars.k_full), 0, abortp);
+      if (!ok) record_timeout(p.status, 22);
+      for (int i = i_begin; i < p.nq_tiles && ok; ++i) {
+        const int c = i - i_begin;
+        const int st = c % kQStages;
+        ok = mbar_wait(smem_u32(&bars.q_full[st]), (c / kQStages) & 1, abortp);
+        if (!ok) { record_timeout(p.status, 23); break; }
+        tc_fence_after_sync();
+        const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
+        for (int t = 0; t < 2; ++t) {
+          if (!active[t] || i < i_start[t]) continue;
+          const int ct = i - i_start[t];
+          const int buf = ct & 1;
+          if (ct >= 2) {
+            ok = mbar_wait(smem_u32(&bars.s_empty[t][buf]), ((ct >> 1) - 1) & 1, abortp);
+            if (!ok) { record_timeout(p.status, 24); break; }
+            tc_fence_after_sync();
+          }
+          const uint64_t kdesc = umma_smem_desc_sw128(sK + t * kTileBytes, 16, 1024);
+          const uint32_t tS = tbase + (t * 2 + buf) * 128;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+            umma_ss(tS, kdesc + off, qdesc + off, idesc, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars.s_full[t][buf]));
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&bars.q_empty[st]));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ one thread per key
+    const int t = (warp - 4) >> 2;
+    const int wq = warp & 3;
+    const int key = kv0[t] + wq * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float scale = p.scale_log2;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+    bool ok = true;
+    const float* er_col = nullptr;
+    if constexpr (kMode == 2) {
+      er_col = p.exp_rand + static_cast<int64_t>(b) * p.er_sb + static_cast<int64_t>(h) * p.er_sh +
+               min(key, p.Skv - 1);
+    }
+
+    if (active[t]) {
+      for (int i = i_begin; i < p.nq_tiles; ++i) {
+        const int c = i - i_begin;
+        const int st = c % kQStages;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_full[st]), (c / kQStages) & 1, abortp));
+        if (!ok) { if (lane == 0) record_timeout(p.status, 25); break; }
+        if (i >= i_start[t]) {
+          const int ct = i - i_start[t];
+          const int buf = ct & 1;
+          ok = __all_sync(0xffffffffu,
+                          mbar_wait(smem_u32(&bars.s_full[t][buf]), (ct >> 1) & 1, abortp));
+          if (!ok) { if (lane == 0) record_timeout(p.status, 26); break; }
+          tc_fence_after_sync();
+          const uint32_t tS = tbase + lane_base + (t * 2 + buf) * 128;
+          float s[128];
+          {
+            uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(s);
+            tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
+            tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
+            tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&u[64]));
+            tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&u[96]));
+            tmem_wait_ld();
+          }
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&bars.s_empty[t][buf]));
+
+          // query c of this tile sees `key` iff key <= (i*128 + c) + diag_off
+          const int first_visible = p.causal ? key - p.diag_off - i * kTile : 0;
+          const bool tile_has_mask = p.causal && (kv0[t] + kTile - 1 - p.diag_off > i * kTile);
+          const float4* lse4 = reinterpret_cast<const float4*>(lse_s[st]);
+#pragma unroll
+          for (int g = 0; g < 32; ++g) {
+            const float4 L = lse4[g];
+            const float lv[4] = {L.x, L.y, L.z, L.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int cc = g * 4 + e;
+              float x;
+              if constexpr (kMode == 2) {
+                const int qi = min(i * kTile + cc, p.Sq - 1);
+                const float er = __ldg(er_col + static_cast<int64_t>(qi) * p.er_sq);
+                x = fmaf(s[cc], scale, fmaf(lg2(er), -p.inv_tau, -lv[e]));
+              } else {
+                x = fmaf(s[cc], scale, -lv[e]);
+              }
+              float pv = ex2(x);
+              if (tile_has_mask) pv = (cc < first_visible) ? 0.f : pv;
+              acc[e] += pv;
+              if constexpr (kMode == 1) acc2[e] = fmaf(pv, pv, acc2[e]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.q_empty[st]));
+      }
+      if (ok && key < p.Skv) {
+        const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
+        p.score[o] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        if constexpr (kMode == 1) p.score_sq[o] = (acc2[0] + acc2[1]) + (acc2[2] + acc2[3]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Keyformer row pass: lse2'[row] = log2 sum_j exp2(((s_ij*scale + g_ij)/tau) * log2e)
+// One CTA per 128 query rows; one thread per row; K tiles stream through a ring.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRsStages = 4;
+constexpr int kRsThreads = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 rows
+constexpr uint32_t kRsSmemBytes = (1 + kRsStages) * kTileBytes + 1024;
+
+struct RsBars {
+  uint64_t q_full;
+  uint64_t k_full[kRsStages], k_empty[kRsStages];
+  uint64_t s_full[2], s_empty[2];
+};
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kRsThreads, 1)
+kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const ColParams p, float* lse_out) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) RsBars bars;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_s;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = smem_base;
+  const uint32_t sK = smem_base + kTileBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile uint32_t* abortp = &abort_s;
+  const int bh_count = p.B * p.H;
+  const int qt = p.nq_tiles - 1 - static_cast<int>(blockIdx.x) / bh_count;
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int b = bh / p.H, h = bh % p.H;
+  const int q0 = qt * kTile;
+  int last = p.Skv - 1;
+  if (p.causal) last = min(last, min(q0 + kTile - 1, p.Sq - 1) + p.diag_off);
+  const int n_kv = last / kTile + 1;
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&bars.q_full), 1);
+    for (int i = 0; i < kRsStages; ++i) {
+      mbar_init(smem_u32(&bars.k_full[i]), 1);
+      mbar_init(smem_u32(&bars.k_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.s_full[i]), 1);
+      mbar_init(smem_u32(&bars.s_empty[i]), 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_s), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      {
+        const uint32_t bar = smem_u32(&bars.q_full);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sQ, &map_q, bar, 0, h, q0, b);
+        tma_load_4d(sQ + kHalfBytes, &map_q, bar, 64, h, q0, b);
+      }
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j % kRsStages;
+        const uint32_t use = static_cast<uint32_t>(j / kRsStages);
+        if (use > 0 && !mbar_wait(smem_u32(&bars.k_empty[st]), (use - 1) & 1, abortp)) {
+          record_timeout(p.status, 31);
+          break;
+        }
+        const uint32_t bar = smem_u32(&bars.k_full[st]);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, h, j * kTile, b);
+        tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+      constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
+      bool ok = mbar_wait(smem_u32(&bars.q_full), 0, abortp);
+      if (!ok) record_timeout(p.status, 32);
+      const uint64_t qdesc = umma_smem_desc_sw128(sQ, 16, 1024);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j % kRsStages, buf = j & 1;
+        ok = mbar_wait(smem_u32(&bars.k_full[st]), (j / kRsStages) & 1, abortp);
+        if (!ok) { record_timeout(p.status, 33); break; }
+        if (j >= 2) {
+          ok = mbar_wait(smem_u32(&bars.s_empty[buf]), ((j >> 1) - 1) & 1, abortp);
+          if (!ok) { record_timeout(p.status, 34); break; }
+        }
+        tc_fence_after_sync();
+        const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+          umma_ss(tbase + buf * 128, qdesc + off, kdesc + off, idesc, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars.s_full[buf]));
+        umma_commit(smem_u32(&bars.k_empty[st]));
+      }
+    }
+  } else {
+    const int wq = warp & 3;  // warps 2,3,4,5 -> lane quarters 2,3,0,1
+    const int row = q0 + wq * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    int lim = p.Skv - 1;
+    if (p.causal) lim = min(lim, row + p.diag_off);
+    const float scale = p.scale_log2;
+    const float* er_row = p.exp_rand + static_cast<int64_t>(b) * p.er_sb +
+                          static_cast<int64_t>(h) * p.er_sh +
+                          static_cast<int64_t>(min(row, p.Sq - 1)) * p.er_sq;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int buf = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[buf]), (j >> 1) & 1, abortp));
+      if (!ok) { if (lane == 0) record_timeout(p.status, 35); break; }
+      tc_fence_after_sync();
+      const int thr = lim - j * kTile;  // columns > thr are masked
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t u[32];
+        tmem_ld32(tbase + lane_base + buf * 128 + c4 * 32, u);
+        tmem_wait_ld();
+        float x[32];
+        float mt = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int cc = c4 * 32 + e;
+          const int kj = min(j * kTile + cc, p.Skv - 1);
+          const float er = __ldg(er_row + kj);
+          const float v = fmaf(__uint_as_float(u[e]), scale, -lg2(er) * p.inv_tau);
+          x[e] = (cc > thr) ? -INFINITY : v;
+          mt = fmaxf(mt, x[e]);
+        }
+        const float m_new = fmaxf(m, mt);
+        if (m_new > -INFINITY) {
+          l *= ex2(m - m_new);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) l += ex2(x[e] - m_new);
+          m = m_new;
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars.s_empty[buf]));
+    }
+    if (ok && row < p.Sq) lse_out[(static_cast<size_t>(b) * p.H + h) * p.Sq + row] = m + log2f(l);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, 256);
+  }
+}
+
+ColParams make_params(const ScoreArgs& a, const AttnShape& s) {
+  ColParams p;
+  p.B = s.B;
+  p.H = s.H;
+  p.Sq = s.Sq;
+  p.Skv = s.Skv;
+  p.causal = s.causal;
+  p.diag_off = s.Skv - s.Sq;
+  p.nq_tiles = (s.Sq + kTile - 1) / kTile;
+  const float log2e = 1.4426950408889634f;
+  p.inv_tau = 1.0f;
+  p.scale_log2 = s.softmax_scale * log2e;
+  if (a.mode == ASUKA_SCORE_PERTURBED) {
+    p.inv_tau = 1.0f / a.tau;
+    p.scale_log2 = s.softmax_scale * log2e / a.tau;
+  }
+  p.lse2 = a.lse2;
+  p.score = a.score;
+  p.score_sq = a.score_sq;
+  p.exp_rand = a.exp_rand;
+  p.er_sb = a.er_stride_b;
+  p.er_sh = a.er_stride_h;
+  p.er_sq = a.er_stride_q;
+  p.status = device_status_words();
+  return p;
+}
+
+}  // namespace
+
+cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
+                              const AttnShape& s, cudaStream_t stream) {
+  const ColParams p = make_params(a, s);
+  const int n_kvb = (s.Skv + 2 * kTile - 1) / (2 * kTile);
+  const dim3 grid(static_cast<unsigned>(n_kvb) * s.B * s.H);
+  void (*kern)(CUtensorMap, CUtensorMap, ColParams) = nullptr;
+  if (a.mode == ASUKA_SCORE_SUM) kern = s.bf16 ? col_scores_kernel<true, 0> : col_scores_kernel<false, 0>;
+  else if (a.mode == ASUKA_SCORE_SUM_SQ) kern = s.bf16 ? col_scores_kernel<true, 1> : col_scores_kernel<false, 1>;
+  else kern = s.bf16 ? col_scores_kernel<true, 2> : col_scores_kernel<false, 2>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, p);
+  count_launch();
+  return cudaPeekAtLastError();
+}
+
+cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
+                              float* lse2_out, const AttnShape& s, cudaStream_t stream) {
+  const ColParams p = make_params(a, s);
+  const dim3 grid(static_cast<unsigned>(p.nq_tiles) * s.B * s.H);
+  auto kern = s.bf16 ? kf_rowstat_kernel<true> : kf_rowstat_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kRsSmemBytes);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kRsThreads, kRsSmemBytes, stream>>>(mq, mk, p, lse2_out);
+  count_launch();
+  return cudaPeekAtLastError();
+}
+
+}  // namespace asuka
