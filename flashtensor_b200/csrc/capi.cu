@@ -248,6 +248,58 @@ int select_impl(const asuka_select_params* p, cudaStream_t stream) {
   return map_cuda(launch_select(a, stream));
 }
 
+int prep_sima(const asuka_sima_params* p, SimaShape* sh) {
+  if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (!is_16bit(p->q.dtype)) return p->q.ptr == nullptr ? ASUKA_ERR_NULL_POINTER : ASUKA_ERR_BAD_DTYPE;
+  int r;
+  if ((r = check_bshd(p->q, p->q.dtype)) != ASUKA_OK) return r;
+  if ((r = check_bshd(p->k, p->q.dtype)) != ASUKA_OK) return r;
+  if ((r = check_bshd(p->v, p->q.dtype)) != ASUKA_OK) return r;
+  for (int i = 0; i < 4; ++i)
+    if (p->k.shape[i] != p->q.shape[i] || p->v.shape[i] != p->q.shape[i]) return ASUKA_ERR_BAD_SHAPE;
+  sh->B = static_cast<int>(p->q.shape[0]);
+  sh->S = static_cast<int>(p->q.shape[1]);
+  sh->H = static_cast<int>(p->q.shape[2]);
+  sh->bf16 = p->q.dtype == ASUKA_BF16;
+  sh->out_f32 = p->out.dtype == ASUKA_F32;
+  if (static_cast<int64_t>(sh->B) * sh->H > (1 << 20)) return ASUKA_ERR_TOO_LARGE;
+  return ASUKA_OK;
+}
+
+int sima_impl(const asuka_sima_params* p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  SimaShape sh;
+  int r = prep_sima(p, &sh);
+  if (r != ASUKA_OK) return r;
+  if (sh.out_f32) {
+    const asuka_tensor& o = p->out;
+    if (o.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
+    if (o.ndim != 4) return ASUKA_ERR_BAD_SHAPE;
+    for (int i = 0; i < 4; ++i)
+      if (o.shape[i] != p->q.shape[i]) return ASUKA_ERR_BAD_SHAPE;
+    if (o.stride[3] != 1) return ASUKA_ERR_BAD_STRIDE;
+    for (int i = 0; i < 3; ++i)
+      if (o.stride[i] <= 0 || (o.stride[i] % 4) != 0) return ASUKA_ERR_BAD_STRIDE;
+    if ((reinterpret_cast<uintptr_t>(o.ptr) & 15u) != 0) return ASUKA_ERR_MISALIGNED;
+  } else {
+    if ((r = check_bshd(p->out, p->q.dtype)) != ASUKA_OK) return r;
+    for (int i = 0; i < 4; ++i)
+      if (p->out.shape[i] != p->q.shape[i]) return ASUKA_ERR_BAD_SHAPE;
+  }
+  if (ws == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return ASUKA_ERR_MISALIGNED;
+  if (ws_bytes < sima_workspace_bytes(sh)) return ASUKA_ERR_WORKSPACE_TOO_SMALL;
+  if ((r = check_arch()) != ASUKA_OK) return r;
+  CUtensorMap mq, mk, mv, mo;
+  if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k)) || (r = make_map(&mv, p->v))) return r;
+  if (!sh.out_f32) {
+    if ((r = make_map(&mo, p->out))) return r;
+  } else {
+    mo = mq;
+  }
+  return map_cuda(launch_sima(mq, mk, mv, mo, p->out.ptr, p->out.stride[0], p->out.stride[1],
+                              p->out.stride[2], ws, sh, stream));
+}
+
 // forward + column scores (+ selection) on one stream; the row statistic lives in `ws`
 enum CaseKind { CASE_H2O, CASE_ROCO, CASE_KF };
 
@@ -395,6 +447,19 @@ int asuka_b200_keyformer_rowstat(const asuka_score_params* p, asuka_stream strea
 
 int asuka_b200_select_topk(const asuka_select_params* p, asuka_stream stream) {
   return select_impl(p, static_cast<cudaStream_t>(stream));
+}
+
+int asuka_b200_sima_workspace_bytes(const asuka_sima_params* p, size_t* bytes) {
+  if (bytes == nullptr) return ASUKA_ERR_NULL_POINTER;
+  SimaShape sh;
+  int r = prep_sima(p, &sh);
+  if (r != ASUKA_OK) return r;
+  *bytes = sima_workspace_bytes(sh);
+  return ASUKA_OK;
+}
+
+int asuka_b200_sima_fwd(const asuka_sima_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
+  return sima_impl(p, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes) {

@@ -1,0 +1,597 @@
+// SimA softmax-free attention for sm_100a:
+//   Qn = Q / sum_s |Q|,  Kn = K / sum_s |K|  (per channel, over the sequence; no epsilon),
+//   out = Qn (Kn^T V), non-causal.
+// Replaces the kernels the Asuka pipeline generates for bench/sima.mlir:13-17, with the L1
+// normalisation of lib/Dialect/Asuka/Transforms/LowerComplexReduce.cpp:44-69.
+//
+// Algebra: out[s,e] = sum_d Q[s,d] * M'[d,e] with M'[d,e] = (sum_s K[s,d] V[s,e]) / (ck[d] cq[d]),
+// so the sequence is streamed twice and no S x S tensor exists:
+//   1. sima_stats_kernel   every CTA streams a slab of the sequence of one (batch, head): K^T V on
+//                          tcgen05 (both operands MN-major straight from the TMA tiles), and the
+//                          column sums of |K| and |Q| with 128-bit shared-memory loads.  Partial
+//                          results go to the workspace.
+//   2. sima_reduce_kernel  sums the partials in a fixed order, divides by ck*cq, and writes M'^T in
+//                          the 16-bit input type scaled by a per-head power of two (the entries are
+//                          ~1e-6, far below fp16's normal range), plus the inverse scale.
+//   3. sima_out_kernel     streams Q again: out = (Q M'') * inverse scale, tcgen05 with the
+//                          accumulator double-buffered in TMEM, TMA store.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "sm100_ptx.cuh"
+#include "tma_host.h"
+
+namespace asuka {
+using namespace sm100;
+
+namespace {
+
+constexpr int kTile = 128;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;
+constexpr uint32_t kHalfBytes = kTileBytes / 2;
+constexpr int kMElems = 128 * 128;
+
+__device__ __forceinline__ void record_timeout(uint32_t* status, uint32_t site) {
+  atomicAdd(&status[0], 1u);
+  status[1] = site;
+}
+
+struct SimaWs {
+  float* part_m;     // [BH][nchunks][e][d]  partial (K^T V)^T
+  float* part_c;     // [BH][nchunks][2][128] partial ck, cq
+  uint16_t* m16;     // [BH][e][d] scaled M'^T in the input type
+  float* inv_scale;  // [BH]
+};
+
+// ---------------------------------------------------------------------------------------------
+// 1. statistics: partial K^T V, sum|K|, sum|Q| over a slab of the sequence
+// ---------------------------------------------------------------------------------------------
+constexpr int kStThreads = 384;
+constexpr int kStStages = 2;
+constexpr uint32_t kStSmem = kStStages * 3 * kTileBytes + 1024;
+
+struct StatsParams {
+  int B, H, S;
+  int nchunks, tiles_per_chunk, ntiles;
+  SimaWs ws;
+  uint32_t* status;
+};
+
+struct StBars {
+  uint64_t full[kStStages], empty[kStStages], m_done;
+};
+
+template <bool kBF16>
+__device__ __forceinline__ void abs_acc8(const uint4& v, float (&acc)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f;
+    if constexpr (kBF16) {
+      f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    } else {
+      f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    }
+    acc[2 * i] += fabsf(f.x);
+    acc[2 * i + 1] += fabsf(f.y);
+  }
+}
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kStThreads, 1)
+sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const StatsParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) StBars bars;
+  __shared__ float red[2][8][kTile];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_s;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile uint32_t* abortp = &abort_s;
+  const int chunk = static_cast<int>(blockIdx.x) % p.nchunks;
+  const int bh = static_cast<int>(blockIdx.x) / p.nchunks;
+  const int b = bh / p.H, h = bh % p.H;
+  const int tile0 = chunk * p.tiles_per_chunk;
+  const int ntile = max(0, min(p.tiles_per_chunk, p.ntiles - tile0));
+
+  if (tid == 0) {
+    abort_s = 0;
+    for (int i = 0; i < kStStages; ++i) {
+      mbar_init(smem_u32(&bars.full[i]), 1);
+      mbar_init(smem_u32(&bars.empty[i]), 1 + 8);
+    }
+    mbar_init(smem_u32(&bars.m_done), 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_s), 128);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+
+  // stage layout: [K | V | Q] tiles
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < ntile; ++i) {
+        const int st = i % kStStages;
+        const uint32_t use = static_cast<uint32_t>(i / kStStages);
+        if (use > 0 && !mbar_wait(smem_u32(&bars.empty[st]), (use - 1) & 1, abortp)) {
+          record_timeout(p.status, 41);
+          break;
+        }
+        const uint32_t bar = smem_u32(&bars.full[st]);
+        const uint32_t base = smem_base + st * 3 * kTileBytes;
+        const int s0 = (tile0 + i) * kTile;
+        mbar_expect_tx(bar, 3 * kTileBytes);
+        tma_load_4d(base, &map_k, bar, 0, h, s0, b);
+        tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h, s0, b);
+        tma_load_4d(base + kTileBytes, &map_v, bar, 0, h, s0, b);
+        tma_load_4d(base + kTileBytes + kHalfBytes, &map_v, bar, 64, h, s0, b);
+        tma_load_4d(base + 2 * kTileBytes, &map_q, bar, 0, h, s0, b);
+        tma_load_4d(base + 2 * kTileBytes + kHalfBytes, &map_q, bar, 64, h, s0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+      constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_MN_MAJOR, UMMA_MN_MAJOR, 128, 128);
+      bool ok = true;
+      for (int i = 0; i < ntile && ok; ++i) {
+        const int st = i % kStStages;
+        ok = mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp);
+        if (!ok) { record_timeout(p.status, 42); break; }
+        tc_fence_after_sync();
+        const uint32_t base = smem_base + st * 3 * kTileBytes;
+        // M = K^T V: TMEM lane = d, column = e
+        const uint64_t adesc = umma_smem_desc_sw128(base, kHalfBytes, 1024);               // K
+        const uint64_t bdesc = umma_smem_desc_sw128(base + kTileBytes, kHalfBytes, 1024);  // V
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t off = static_cast<uint64_t>(kk * (2048 >> 4));
+          umma_ss(tbase, adesc + off, bdesc + off, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars.empty[st]));
+      }
+      if (ok) umma_commit(smem_u32(&bars.m_done));
+    }
+  } else if (warp >= 4) {
+    // warps 4-7: |K| column sums; warps 8-11: |Q| column sums
+    const int which = (warp - 4) >> 2;  // 0 = K, 1 = Q
+    const int t128 = tid - 128 - which * 128;
+    const int chunk16 = t128 & 15;   // 8 consecutive channels
+    const int rg = t128 >> 4;        // rows rg, rg+8, ...
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bool ok = true;
+    for (int i = 0; i < ntile; ++i) {
+      const int st = i % kStStages;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp));
+      if (!ok) { if (lane == 0) record_timeout(p.status, 43); break; }
+      const uint8_t* tile = smem_gen + st * 3 * kTileBytes + (which ? 2 * kTileBytes : 0) +
+                            (chunk16 >> 3) * kHalfBytes;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const int row = rg + 8 * r;
+        const uint4 v = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
+        abs_acc8<kBF16>(v, acc);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[which][rg][chunk16 * 8 + i] = acc[i];
+    named_bar_sync(1 + which, 128);
+    {
+      float s = 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) s += red[which][g][t128];
+      p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + which) * kTile + t128] = s;
+    }
+    if (which == 0) {
+      // warps 4-7 also drain the accumulator: lane = d, column = e
+      float* dst = p.ws.part_m + (static_cast<size_t>(bh) * p.nchunks + chunk) * kMElems;
+      const int wq = warp & 3;
+      const int d = wq * 32 + lane;
+      if (ntile > 0) {
+        ok = ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.m_done), 0, abortp));
+        if (ok) {
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t u[32];
+            tmem_ld32(tbase + (static_cast<uint32_t>(wq * 32) << 16) + c * 32, u);
+            tmem_wait_ld();
+            // thread d holds M[d][e..]; element (d, e) -> dst[e * 128 + d]: consecutive threads
+            // hit consecutive addresses and the partial is stored transposed, [e][d]
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dst[(c * 32 + i) * kTile + d] = __uint_as_float(u[i]);
+          }
+        } else if (lane == 0) {
+          record_timeout(p.status, 44);
+        }
+      } else {
+        for (int i = 0; i < 128; ++i) dst[i * kTile + d] = 0.f;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, 128);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2. reduce partials, normalise, scale into the 16-bit type.  part_m and the output m16 are
+//    both stored [e][d] (d contiguous): the K-major B operand of step 3.
+// ---------------------------------------------------------------------------------------------
+template <bool kBF16>
+__global__ void __launch_bounds__(256, 1) sima_reduce_kernel(const StatsParams p) {
+  __shared__ float inv_c[kTile];
+  __shared__ float wmax[8];
+  __shared__ float s_scale;
+  const int bh = blockIdx.x, tid = threadIdx.x;
+  const float* pc = p.ws.part_c + static_cast<size_t>(bh) * p.nchunks * 2 * kTile;
+  const float* pm = p.ws.part_m + static_cast<size_t>(bh) * p.nchunks * kMElems;
+  if (tid < kTile) {
+    float ck = 0.f, cq = 0.f;
+    for (int c = 0; c < p.nchunks; ++c) {
+      ck += pc[(c * 2 + 0) * kTile + tid];
+      cq += pc[(c * 2 + 1) * kTile + tid];
+    }
+    inv_c[tid] = __fdiv_rn(1.0f, __fmul_rn(ck, cq));
+  }
+  __syncthreads();
+  float vals[kMElems / 256];
+  float amax = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMElems / 256; ++it) {
+    const int idx = it * 256 + tid;  // = e * 128 + d
+    float m = 0.f;
+    for (int c = 0; c < p.nchunks; ++c) m += pm[static_cast<size_t>(c) * kMElems + idx];
+    m *= inv_c[idx & 127];
+    vals[it] = m;
+    amax = fmaxf(amax, fabsf(m));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((tid & 31) == 0) wmax[tid >> 5] = amax;
+  __syncthreads();
+  if (tid == 0) {
+    float a = 0.f;
+    for (int i = 0; i < 8; ++i) a = fmaxf(a, wmax[i]);
+    float sc = 1.f;
+    if (a > 0.f && a < INFINITY) {
+      int ex;
+      frexpf(a, &ex);            // a = f * 2^ex, f in [0.5, 1)
+      sc = ldexpf(1.0f, 14 - ex);  // a * sc in [2^13, 2^14)
+    }
+    s_scale = sc;
+    p.ws.inv_scale[bh] = 1.0f / sc;
+  }
+  __syncthreads();
+  const float sc = s_scale;
+  uint16_t* dst = p.ws.m16 + static_cast<size_t>(bh) * kMElems;
+#pragma unroll
+  for (int it = 0; it < kMElems / 256; ++it) {
+    const int idx = it * 256 + tid;
+    const float v = vals[it] * sc;
+    uint16_t bits;
+    if constexpr (kBF16) {
+      __nv_bfloat16 hb = __float2bfloat16_rn(v);
+      bits = *reinterpret_cast<uint16_t*>(&hb);
+    } else {
+      __half hh = __float2half_rn(v);
+      bits = *reinterpret_cast<uint16_t*>(&hh);
+    }
+    dst[idx] = bits;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 3. out = (Q M'') * inv_scale
+// ---------------------------------------------------------------------------------------------
+constexpr int kOutThreads = 256;  // warp 0 producer, warp 1 MMA, warps 4-7 epilogue
+constexpr int kOutStages = 3;
+constexpr uint32_t kOutSmem = (1 + kOutStages + 2) * kTileBytes + 1024;
+
+struct OutParams {
+  int B, H, S;
+  int ntiles, tiles_per_cta, nqchunks;
+  const float* inv_scale;
+  float* out_f32;  // non-null selects the f32 output path
+  int64_t o_sb, o_ss, o_sh;
+  uint32_t* status;
+};
+
+struct OutBars {
+  uint64_t m_full, q_full[kOutStages], q_empty[kOutStages], acc_full[2], acc_empty[2];
+};
+
+template <bool kBF16, bool kOutF32>
+__global__ void __launch_bounds__(kOutThreads, 1)
+sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_m,
+                const __grid_constant__ CUtensorMap map_o, const OutParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) OutBars bars;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_s;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sM = smem_base;
+  const uint32_t sQ = smem_base + kTileBytes;
+  const uint32_t sO = sQ + kOutStages * kTileBytes;  // two 32 KB staging buffers (one 64 KB for f32)
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile uint32_t* abortp = &abort_s;
+  const int qc = static_cast<int>(blockIdx.x) % p.nqchunks;
+  const int bh = static_cast<int>(blockIdx.x) / p.nqchunks;
+  const int b = bh / p.H, h = bh % p.H;
+  const int tile0 = qc * p.tiles_per_cta;
+  const int ntile = max(0, min(p.tiles_per_cta, p.ntiles - tile0));
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&bars.m_full), 1);
+    for (int i = 0; i < kOutStages; ++i) {
+      mbar_init(smem_u32(&bars.q_full[i]), 1);
+      mbar_init(smem_u32(&bars.q_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.acc_full[i]), 1);
+      mbar_init(smem_u32(&bars.acc_empty[i]), 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_s), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0 && ntile > 0) {
+      {
+        const uint32_t bar = smem_u32(&bars.m_full);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sM, &map_m, bar, 0, 0, bh * kTile, 0);
+        tma_load_4d(sM + kHalfBytes, &map_m, bar, 64, 0, bh * kTile, 0);
+      }
+      for (int i = 0; i < ntile; ++i) {
+        const int st = i % kOutStages;
+        const uint32_t use = static_cast<uint32_t>(i / kOutStages);
+        if (use > 0 && !mbar_wait(smem_u32(&bars.q_empty[st]), (use - 1) & 1, abortp)) {
+          record_timeout(p.status, 51);
+          break;
+        }
+        const uint32_t bar = smem_u32(&bars.q_full[st]);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sQ + st * kTileBytes, &map_q, bar, 0, h, (tile0 + i) * kTile, b);
+        tma_load_4d(sQ + st * kTileBytes + kHalfBytes, &map_q, bar, 64, h, (tile0 + i) * kTile, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && ntile > 0) {
+      constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+      constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
+      bool ok = mbar_wait(smem_u32(&bars.m_full), 0, abortp);
+      if (!ok) record_timeout(p.status, 52);
+      const uint64_t mdesc = umma_smem_desc_sw128(sM, 16, 1024);
+      for (int i = 0; i < ntile && ok; ++i) {
+        const int st = i % kOutStages, buf = i & 1;
+        ok = mbar_wait(smem_u32(&bars.q_full[st]), (i / kOutStages) & 1, abortp);
+        if (!ok) { record_timeout(p.status, 53); break; }
+        if (i >= 2) {
+          ok = mbar_wait(smem_u32(&bars.acc_empty[buf]), ((i >> 1) - 1) & 1, abortp);
+          if (!ok) { record_timeout(p.status, 54); break; }
+        }
+        tc_fence_after_sync();
+        const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+          umma_ss(tbase + buf * 128, qdesc + off, mdesc + off, idesc, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars.acc_full[buf]));
+        umma_commit(smem_u32(&bars.q_empty[st]));
+      }
+    }
+  } else if (warp >= 4) {
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;  // row of the tile
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float inv_sc = p.inv_scale[bh];
+    bool ok = true;
+    for (int i = 0; i < ntile; ++i) {
+      const int buf = i & 1;
+      const int s0 = (tile0 + i) * kTile;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_full[buf]), (i >> 1) & 1, abortp));
+      if (!ok) { if (lane == 0) record_timeout(p.status, 55); break; }
+      tc_fence_after_sync();
+      // the staging buffer about to be overwritten must have been read by its previous store
+      if constexpr (!kOutF32) {
+        if (tid == 128) tma_store_wait_read_n<1>();
+      }
+      named_bar_sync(1, 128);
+      uint8_t* stage = smem_gen + (sO - smem_base) + (kOutF32 ? 0 : buf * kTileBytes);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t u[32];
+        tmem_ld32(tbase + lane_base + buf * 128 + c * 32, u);
+        tmem_wait_ld();
+        if constexpr (kOutF32) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 v;
+            v.x = __uint_as_float(u[g * 4 + 0]) * inv_sc;
+            v.y = __uint_as_float(u[g * 4 + 1]) * inv_sc;
+            v.z = __uint_as_float(u[g * 4 + 2]) * inv_sc;
+            v.w = __uint_as_float(u[g * 4 + 3]) * inv_sc;
+            const int chunk = c * 8 + g;  // 16-byte chunk of the 512-byte row
+            *reinterpret_cast<float4*>(stage + r * 512 + ((chunk ^ (r & 31)) << 4)) = v;
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float lo = __uint_as_float(u[g * 8 + 2 * q]) * inv_sc;
+              const float hi = __uint_as_float(u[g * 8 + 2 * q + 1]) * inv_sc;
+              if constexpr (kBF16) {
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi);
+                w[q] = *reinterpret_cast<uint32_t*>(&t2);
+              } else {
+                __half2 t2 = __floats2half2_rn(lo, hi);
+                w[q] = *reinterpret_cast<uint32_t*>(&t2);
+              }
+            }
+            const int chunk = c * 4 + g;
+            *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes + sw128_offset(r, chunk & 7)) =
+                make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+      if constexpr (kOutF32) {
+        named_bar_sync(1, 128);
+        // coalesced copy-out: every warp writes whole 512-byte rows
+        for (int rr = wq; rr < kTile; rr += 4) {
+          const int s = s0 + rr;
+          if (s < p.S) {
+            const float4 v = *reinterpret_cast<const float4*>(stage + rr * 512 + (lane << 4));
+            const int chunk = lane ^ (rr & 31);
+            float* o = p.out_f32 + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(s) * p.o_ss +
+                       static_cast<int64_t>(h) * p.o_sh + chunk * 4;
+            *reinterpret_cast<float4*>(o) = v;
+          }
+        }
+      } else {
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (tid == 128) {
+          tma_store_4d(&map_o, sO + buf * kTileBytes, 0, h, s0, b);
+          tma_store_4d(&map_o, sO + buf * kTileBytes + kHalfBytes, 64, h, s0, b);
+          tma_store_commit();
+        }
+      }
+    }
+    if constexpr (!kOutF32) {
+      if (tid == 128) tma_store_wait_read();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, 256);
+  }
+}
+
+size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+struct Plan {
+  int ntiles, nchunks, tiles_per_chunk;
+  size_t off_pm, off_pc, off_m16, off_sc, total;
+};
+
+Plan make_plan(const SimaShape& s) {
+  Plan pl;
+  const int bh = s.B * s.H;
+  pl.ntiles = (s.S + kTile - 1) / kTile;
+  int want = (1024 + bh - 1) / bh;
+  if (want < 1) want = 1;
+  if (want > 16) want = 16;
+  if (want > pl.ntiles) want = pl.ntiles;
+  pl.tiles_per_chunk = (pl.ntiles + want - 1) / want;
+  pl.nchunks = (pl.ntiles + pl.tiles_per_chunk - 1) / pl.tiles_per_chunk;
+  size_t off = 0;
+  pl.off_pm = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * kMElems * 4);
+  pl.off_pc = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * 2 * kTile * 4);
+  pl.off_m16 = off; off = align256(off + static_cast<size_t>(bh) * kMElems * 2);
+  pl.off_sc = off; off = align256(off + static_cast<size_t>(bh) * 4);
+  pl.total = off;
+  return pl;
+}
+
+}  // namespace
+
+size_t sima_workspace_bytes(const SimaShape& s) { return make_plan(s).total; }
+
+cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                        const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
+                        int64_t out_stride_s, int64_t out_stride_h, void* ws, const SimaShape& s,
+                        cudaStream_t stream) {
+  const Plan pl = make_plan(s);
+  const int bh = s.B * s.H;
+  uint8_t* w = static_cast<uint8_t*>(ws);
+  StatsParams sp;
+  sp.B = s.B; sp.H = s.H; sp.S = s.S;
+  sp.nchunks = pl.nchunks; sp.tiles_per_chunk = pl.tiles_per_chunk; sp.ntiles = pl.ntiles;
+  sp.ws.part_m = reinterpret_cast<float*>(w + pl.off_pm);
+  sp.ws.part_c = reinterpret_cast<float*>(w + pl.off_pc);
+  sp.ws.m16 = reinterpret_cast<uint16_t*>(w + pl.off_m16);
+  sp.ws.inv_scale = reinterpret_cast<float*>(w + pl.off_sc);
+  sp.status = device_status_words();
+
+  cudaError_t e;
+  {
+    auto kern = s.bf16 ? sima_stats_kernel<true> : sima_stats_kernel<false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmem);
+    if (e != cudaSuccess) return e;
+    kern<<<static_cast<unsigned>(bh) * pl.nchunks, kStThreads, kStSmem, stream>>>(mq, mk, mv, sp);
+    count_launch();
+    if ((e = cudaPeekAtLastError()) != cudaSuccess) return e;
+  }
+  {
+    auto kern = s.bf16 ? sima_reduce_kernel<true> : sima_reduce_kernel<false>;
+    kern<<<bh, 256, 0, stream>>>(sp);
+    count_launch();
+    if ((e = cudaPeekAtLastError()) != cudaSuccess) return e;
+  }
+  {
+    CUtensorMap mm;
+    if (tma_host::make_bshd_map(&mm, sp.ws.m16, s.bf16, 1, static_cast<int64_t>(bh) * kTile, 1, kTile,
+                                static_cast<int64_t>(bh) * kMElems, kTile, kTile, 128) != 0)
+      return cudaErrorInvalidValue;
+    OutParams op;
+    op.B = s.B; op.H = s.H; op.S = s.S;
+    op.ntiles = pl.ntiles;
+    // enough CTAs for ~7 waves, at least 2 tiles each so that M'' is amortised
+    int nq = (1024 + bh - 1) / bh;
+    if (nq < 1) nq = 1;
+    if (nq > pl.ntiles) nq = pl.ntiles;
+    op.tiles_per_cta = (pl.ntiles + nq - 1) / nq;
+    op.nqchunks = (pl.ntiles + op.tiles_per_cta - 1) / op.tiles_per_cta;
+    op.inv_scale = sp.ws.inv_scale;
+    op.out_f32 = s.out_f32 ? static_cast<float*>(out_ptr) : nullptr;
+    op.o_sb = out_stride_b; op.o_ss = out_stride_s; op.o_sh = out_stride_h;
+    op.status = sp.status;
+    void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, OutParams);
+    if (s.out_f32) kern = s.bf16 ? sima_out_kernel<true, true> : sima_out_kernel<false, true>;
+    else kern = s.bf16 ? sima_out_kernel<true, false> : sima_out_kernel<false, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kOutSmem);
+    if (e != cudaSuccess) return e;
+    kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads, kOutSmem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);
+    count_launch();
+    e = cudaPeekAtLastError();
+  }
+  return e;
+}
+
+}  // namespace asuka
