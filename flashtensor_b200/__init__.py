@@ -1,0 +1,10 @@
+"""flashtensor_b200: hand-written sm_100a kernels for the fused attention programs of
+FlashTensor/Asuka (plain causal attention, H2O, Keyformer, RoCo, SimA), behind the reference's
+per-case callables and back-end plug-in interface.  The CUDA library is mandatory: importing the
+operator layer without it raises."""
+from . import _lib
+from .builder import B200Builder, Builder
+from .cases import CASES, Attn, H2O, KeyFormer, RoCo, SimA, get_model
+
+__all__ = ["Attn", "H2O", "KeyFormer", "RoCo", "SimA", "CASES", "get_model", "Builder",
+           "B200Builder", "_lib"]

@@ -1,0 +1,155 @@
+"""Per-case callables with the reference's signatures.
+
+Each class mirrors the eager module of the same name in the reference (``cases/kernels/attn.py``,
+``h2o.py``, ``kf.py``, ``roco.py``): same constructor arguments, same ``forward`` arguments and
+return order, same ``prepare`` dictionary, and a module-level ``get_model``-style factory.  The
+body of ``forward`` is the hand-written sm_100a kernel library instead of PyTorch eager or a
+generated Triton kernel.  ``SimA`` has no Python counterpart in the reference (only
+``bench/sima.mlir``); its signature follows the other cases.
+
+The ``select`` methods are additions the benchmark configuration defines (the reference stops at
+the scores): they return the kept key indices as ascending int32.
+"""
+import torch
+
+from . import ops
+
+
+class _Case:
+  output_names = ["out"]
+
+  def __init__(self, kv_head_num=32, head_num=32, head_dim=128):
+    if head_dim != 128:
+      raise ValueError("the sm_100a kernels are built for head_dim = 128")
+    self.kv_head_num = kv_head_num
+    self.head_num = head_num
+    self.head_dim = head_dim
+    self.hidden_size = head_num * head_dim
+    self.kv_hidden_size = kv_head_num * head_dim
+    self.group_size = self.head_num // self.kv_head_num
+    # same restriction as the reference's 4-D cases (cases/kernels/h2o.py:16)
+    assert self.group_size == 1
+
+  def __call__(self, *args, **kwargs):
+    return self.forward(*args, **kwargs)
+
+  # nn.Module-style no-ops so that scripts written for the reference keep working
+  def eval(self):
+    return self
+
+  def to(self, *_args, **_kwargs):
+    return self
+
+  def _check(self, q):
+    if q.dim() == 4 and q.shape[2] != self.head_num:
+      raise RuntimeError(f"expected {self.head_num} heads, got {q.shape[2]}")
+
+  def prepare(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):
+    """Random inputs of the case's shapes, as ``prepare`` in cases/kernels/h2o.py:41-58."""
+    device = torch.cuda.current_device() if device is None else device
+    shape_q = (batch_size, q_len, self.head_num, self.head_dim)
+    shape_kv = (batch_size, kv_len, self.head_num, self.head_dim)
+    q = torch.randn(shape_q, dtype=dtype, device=device)
+    k = torch.randn(shape_kv, dtype=dtype, device=device)
+    v = torch.randn(shape_kv, dtype=dtype, device=device)
+    return {"input": {"q": q, "k": k, "v": v}, "output": list(self.output_names)}
+
+
+class Attn(_Case):
+  """cases/kernels/attn.py:7-34.  ``causal=False`` gives ``forward_wo_mask`` of cases/attn.py."""
+  output_names = ["out"]
+
+  def __init__(self, kv_head_num=32, head_num=32, head_dim=128, causal=True):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.causal = causal
+
+  def forward(self, q, k, v):
+    self._check(q)
+    return ops.attn_fwd(q, k, v, causal=self.causal)
+
+
+class H2O(_Case):
+  """cases/kernels/h2o.py:7-38: returns (out, h2o_score [B,H,Skv] f32)."""
+  output_names = ["out", "h2o_score"]
+
+  def __init__(self, kv_head_num=32, head_num=32, head_dim=128, causal=True):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.causal = causal
+
+  def forward(self, q, k, v):
+    self._check(q)
+    return ops.h2o(q, k, v, causal=self.causal)
+
+  def select(self, q, k, v, k_keep, recent):
+    """(out, h2o_score, idx): keep the `k_keep` heaviest keys of [0, S-recent) plus the last
+    `recent` keys."""
+    self._check(q)
+    return ops.h2o(q, k, v, causal=self.causal, k_keep=k_keep, recent=recent)
+
+
+class KeyFormer(_Case):
+  """cases/kernels/kf.py:7-42: returns (out, kf_score); ``tau`` is a constructor constant."""
+  output_names = ["out", "kf_score"]
+
+  def __init__(self, tau=1.5, kv_head_num=32, head_num=32, head_dim=128, causal=True):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.tau = tau
+    self.causal = causal
+
+  def forward(self, q, k, v, exp_rand):
+    self._check(q)
+    return ops.keyformer(q, k, v, exp_rand, tau=self.tau, causal=self.causal)
+
+  def select(self, q, k, v, exp_rand, k_keep):
+    self._check(q)
+    return ops.keyformer(q, k, v, exp_rand, tau=self.tau, causal=self.causal, k_keep=k_keep)
+
+  def prepare(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):
+    ret = super().prepare(batch_size, q_len, kv_len, dtype, device)
+    q = ret["input"]["q"]
+    # the case's own noise, cases/kernels/kf.py:48
+    ret["input"]["exp_rand"] = 1 + torch.randn(batch_size, self.head_num, q_len, kv_len,
+                                               dtype=torch.float32, device=q.device).abs()
+    return ret
+
+
+class RoCo(_Case):
+  """cases/kernels/roco.py:7-48: returns (out, roco_score, roco_sq_score)."""
+  output_names = ["out", "roco_score", "roco_sq_score"]
+
+  def __init__(self, kv_head_num=32, head_num=32, head_dim=128, causal=True):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.causal = causal
+
+  def forward(self, q, k, v):
+    self._check(q)
+    return ops.roco(q, k, v, causal=self.causal)
+
+  def select(self, q, k, v, k_keep):
+    """(out, roco_score, roco_sq_score, idx): the `k_keep` keys of largest mean probability,
+    ties broken by larger standard deviation, then lower index."""
+    self._check(q)
+    return ops.roco(q, k, v, causal=self.causal, k_keep=k_keep)
+
+
+class SimA(_Case):
+  """bench/sima.mlir:13-17: out = L1norm(q) (L1norm(k)^T v), normalised over the sequence axis."""
+  output_names = ["out"]
+
+  def forward(self, q, k, v):
+    self._check(q)
+    return ops.sima_fwd(q, k, v)
+
+  def prepare(self, batch_size=8, q_len=8192, kv_len=None, dtype=torch.float16, device=None):
+    ret = super().prepare(batch_size, q_len, q_len, dtype, device)
+    v = ret["input"]["v"]
+    ret["input"]["v"] = (torch.rand(v.shape, dtype=torch.float32, device=v.device) * 2 - 1).to(dtype)
+    return ret
+
+
+CASES = {"Attn": Attn, "H2O": H2O, "KeyFormer": KeyFormer, "RoCo": RoCo, "SimA": SimA}
+
+
+def get_model(name="H2O", **kwargs):
+  """Factory in the spirit of each reference module's ``get_model()``."""
+  return CASES[name](**kwargs)

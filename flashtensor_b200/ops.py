@@ -50,7 +50,11 @@ def _as4d(t):
 def _same_device(*ts):
   dev = ts[0].device
   for t in ts:
-    if t is not None and t.device != dev:
+    if t is None:
+      continue
+    if not t.is_cuda:
+      raise RuntimeError("asuka_b200 kernels run on CUDA tensors only; there is no CPU path")
+    if t.device != dev:
       raise RuntimeError("all tensors must be on the same device")
 
 

@@ -1,0 +1,334 @@
+"""GPU parity: the CUDA kernels, called through the C ABI (ctypes), against
+ (1) fixtures produced by the reference's own eager modules (tests/golden/),
+ (2) the CPU oracle on seeded inputs, including the edge cases,
+ (3) size-independent properties at the benchmark's full sizes.
+
+Tolerances are the ones the specification states for fp16/bf16 kernels: outputs and scores within
+max-abs 2e-2 AND scale-relative (max|d| / max|ref|) 1e-2; kept-index sets identical except at ties
+within one fp16 ulp of the k-th key; selection on the kernels' own scores bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_NAMES, load_golden
+from oracle import attn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ABS_TOL = 2e-2
+REL_TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def ops(built_lib):
+  if not torch.cuda.is_available():
+    pytest.fail("the GPU parity tests need a CUDA device")
+  from flashtensor_b200 import ops as _ops
+  return _ops
+
+
+def close(got, ref, what):
+  e = O.errors(got, ref)
+  assert e["abs_max"] <= ABS_TOL, f"{what}: max-abs {e['abs_max']:.3e} > {ABS_TOL}"
+  assert e["scale_rel"] <= REL_TOL, f"{what}: scale-relative {e['scale_rel']:.3e} > {REL_TOL}"
+  assert torch.isfinite(got.float()).all(), f"{what}: non-finite values"
+
+
+def no_timeouts(ops):
+  assert ops.device_status() == (0, 0)
+
+
+# ------------------------------------------------------------------------------------------
+# (1) golden fixtures from the reference
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", GOLDEN_NAMES)
+def test_against_reference_fixture(ops, name):
+  g = load_golden(name)
+  q, k, v = g["q"].cuda(), g["k"].cuda(), g["v"].cuda()
+  if name.startswith("attn"):
+    outs = (ops.attn_fwd(q, k, v),)
+  elif name.startswith("h2o"):
+    outs = ops.h2o(q, k, v)
+  elif name.startswith("kf"):
+    outs = ops.keyformer(q, k, v, g["exp_rand"].cuda(), tau=g["tau"])
+  else:
+    outs = ops.roco(q, k, v)
+  torch.cuda.synchronize()
+  assert len(outs) == len(g["outs"])
+  for i, (got, want) in enumerate(zip(outs, g["outs"])):
+    assert tuple(got.shape) == tuple(want.shape)
+    close(got, want, f"{name} output {i}")
+  no_timeouts(ops)
+
+
+# ------------------------------------------------------------------------------------------
+# (2) oracle parity on seeded inputs
+# ------------------------------------------------------------------------------------------
+SHAPES = [
+    # B, Sq, Skv, H, causal
+    (1, 128, 128, 1, True),
+    (1, 1, 1, 1, True),          # a single token
+    (2, 200, 200, 3, True),      # ragged: not a multiple of the tile
+    (1, 100, 333, 2, True),      # q_len != kv_len, both ragged
+    (1, 128, 640, 2, True),      # chunked prefill: short query block over a long cache
+    (1, 300, 300, 2, False),     # unmasked form (cases/attn.py forward_wo_mask, bench/*.mlir)
+    (1, 257, 257, 1, True),      # one row past a 256-row block
+    (1, 1024, 1024, 4, True),    # configuration C1's shape with fewer heads
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_attn_and_h2o_vs_oracle(ops, shape, dtype):
+  B, Sq, Skv, H, causal = shape
+  q, k, v = O.make_inputs("h2o", B, Sq, Skv, H, 128, dtype, seed=Sq + Skv)
+  ref_out, ref_score = O.h2o(q, k, v, causal)
+  qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+  out = ops.attn_fwd(qd, kd, vd, causal=causal)
+  out2, score = ops.h2o(qd, kd, vd, causal=causal)
+  torch.cuda.synchronize()
+  close(out, ref_out, "attn out")
+  assert torch.equal(out, out2), "H2O's output must be the attention kernel's output"
+  close(score, ref_score, "h2o_score")
+  # every probability row sums to one, so the scores of a head sum to the number of query rows
+  torch.testing.assert_close(score.sum(-1).cpu(), torch.full((B, H), float(Sq)), rtol=1e-4, atol=1e-3)
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 384, 384, 2), (2, 1000, 1000, 3), (1, 200, 456, 2)])
+def test_roco_vs_oracle(ops, shape, dtype):
+  B, Sq, Skv, H = shape
+  q, k, v = O.make_inputs("roco", B, Sq, Skv, H, 128, dtype, seed=7)
+  ref = O.roco(q, k, v)
+  got = ops.roco(q.cuda(), k.cuda(), v.cuda())
+  torch.cuda.synchronize()
+  for g, r, n in zip(got, ref, ("out", "roco_score", "roco_sq_score")):
+    close(g, r, n)
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 256, 256, 2), (2, 640, 640, 2), (1, 130, 300, 1)])
+def test_keyformer_vs_oracle(ops, shape, dtype):
+  B, Sq, Skv, H = shape
+  q, k, v, er = O.make_inputs("keyformer", B, Sq, Skv, H, 128, dtype, seed=9)
+  ref_out, ref_score = O.keyformer(q, k, v, er, tau=1.5)
+  out, score = ops.keyformer(q.cuda(), k.cuda(), v.cuda(), er.cuda(), tau=1.5)
+  torch.cuda.synchronize()
+  close(out, ref_out, "out")
+  close(score, ref_score, "kf_score")
+  torch.testing.assert_close(score.sum(-1).cpu(), torch.full((B, H), float(Sq)), rtol=1e-4, atol=1e-3)
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 128, 1), (2, 1000, 3), (1, 4096, 2), (1, 77, 2)])
+def test_sima_vs_oracle(ops, shape, dtype):
+  B, S, H = shape
+  q, k, v = O.make_inputs("sima", B, S, S, H, 128, dtype, seed=5)
+  ref = O.sima(q, k, v)
+  out16 = ops.sima_fwd(q.cuda(), k.cuda(), v.cuda())
+  out32 = ops.sima_fwd(q.cuda(), k.cuda(), v.cuda(), out_dtype=torch.float32)
+  torch.cuda.synchronize()
+  # outputs are ~1/S: "relative" is scale-relative (element-wise relative error of numbers near
+  # fp16's subnormal range means nothing)
+  close(out32, ref, "sima f32 out")
+  close(out16, ref, "sima 16-bit out")
+  no_timeouts(ops)
+
+
+def test_layouts_strided_and_2d(ops):
+  # heads sliced out of a larger buffer (non-contiguous), and the 2-D [S, H*D] layout of cases/attn.py
+  B, S, H = 2, 256, 4
+  q, k, v = O.make_inputs("h2o", B, S, S, H, 128, torch.float16, seed=3)
+  big = [torch.zeros(B, S, H + 2, 128, dtype=torch.float16, device="cuda") for _ in range(3)]
+  views = []
+  for buf, t in zip(big, (q, k, v)):
+    buf[:, :, 1:H + 1] = t.cuda()
+    views.append(buf[:, :, 1:H + 1])
+  assert not views[0].is_contiguous()
+  ref_out, ref_score = O.h2o(q, k, v)
+  out, score = ops.h2o(*views)
+  close(out, ref_out, "strided out")
+  close(score, ref_score, "strided score")
+  q2, k2, v2 = (t[0].reshape(S, H * 128).cuda() for t in (q, k, v))
+  out2 = ops.attn_fwd(q2, k2, v2)
+  assert out2.shape == (S, H * 128)
+  close(out2.view(1, S, H, 128), O.attn(q[:1], k[:1], v[:1]), "2-D layout out")
+  no_timeouts(ops)
+
+
+def test_per_case_callables_and_builder(ops):
+  import flashtensor_b200 as ft
+  q, k, v, er = O.make_inputs("keyformer", 1, 256, 256, 4, 128, torch.float16, seed=21)
+  qd, kd, vd, erd = q.cuda(), k.cuda(), v.cuda(), er.cuda()
+  out = ft.Attn(head_num=4, kv_head_num=4)(qd, kd, vd)
+  o2, s2 = ft.H2O(head_num=4, kv_head_num=4).forward(qd, kd, vd)
+  o3, s3 = ft.KeyFormer(tau=1.5, head_num=4, kv_head_num=4).forward(qd, kd, vd, erd)
+  o4, s4, sq4 = ft.B200Builder("RoCo", head_num=4, kv_head_num=4).build_callable()(qd, kd, vd)
+  assert torch.equal(out, o2) and torch.equal(out, o3) and torch.equal(out, o4)
+  close(out, O.attn(q, k, v), "Attn")
+  close(s2, O.h2o(q, k, v)[1], "H2O score")
+  close(s3, O.keyformer(q, k, v, er, 1.5)[1], "KeyFormer score")
+  close(sq4, O.roco(q, k, v)[2], "RoCo sq score")
+  prep = ft.H2O(head_num=2, kv_head_num=2).prepare(batch_size=1, q_len=128, kv_len=128)
+  assert prep["output"] == ["out", "h2o_score"] and prep["input"]["q"].shape == (1, 128, 2, 128)
+  with pytest.raises(RuntimeError):
+    ft.H2O(head_num=8, kv_head_num=8)(qd, kd, vd)       # head count mismatch
+
+
+# ------------------------------------------------------------------------------------------
+# selection
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("S,k_keep,recent", [(256, 32, 16), (1024, 128, 64), (4096, 512, 256), (777, 100, 50)])
+def test_h2o_selection(ops, S, k_keep, recent):
+  B, H = 1, 4
+  q, k, v = O.make_inputs("h2o", B, S, S, H, 128, torch.float16, seed=S)
+  out, score, idx = ops.h2o(q.cuda(), k.cuda(), v.cuda(), k_keep=k_keep, recent=recent)
+  torch.cuda.synchronize()
+  idx = idx.cpu().numpy()
+  assert idx.shape == (B, H, k_keep + recent) and idx.dtype == np.int32
+  # integer work on the kernel's own scores: bit-exact against the oracle's rule
+  assert np.array_equal(idx, O.h2o_select(score.cpu().numpy(), k_keep, recent))
+  # against the oracle's scores: identical except inside the one-ulp tie band
+  ref_score = O.h2o(q, k, v)[1].numpy()
+  want = O.h2o_select(ref_score, k_keep, recent)
+  O.check_index_sets(idx[:, :, :k_keep], want[:, :, :k_keep], ref_score, k_keep, S - recent)
+  assert np.array_equal(idx[:, :, k_keep:], want[:, :, k_keep:])
+  no_timeouts(ops)
+
+
+def test_selection_with_many_exact_ties(ops):
+  # constant scores: every key ties; the lowest indices must win, for every k
+  from flashtensor_b200 import _lib
+  score = torch.ones(2, 3, 1000, device="cuda")
+  for k_keep in (1, 7, 999, 1000):
+    idx = ops.select_topk(score, k_keep).cpu().numpy()
+    assert np.array_equal(idx, np.broadcast_to(np.arange(k_keep, dtype=np.int32), (2, 3, k_keep)))
+  # two-level scores with a tie straddling the cut
+  s = torch.zeros(1, 1, 64, device="cuda")
+  s[0, 0, [5, 9, 40]] = 2.0
+  s[0, 0, [3, 20, 21, 50]] = 1.0
+  assert ops.select_topk(s, 5).cpu().tolist() == [[[3, 5, 9, 20, 40]]]
+  idx = ops.select_topk(s, 2, mode=_lib.SELECT_TOPK_RECENT, recent=30).cpu().tolist()[0][0]
+  assert idx == [5, 9] + list(range(34, 64))
+  # denormals, zeros and large values keep their order
+  s = torch.tensor([[[0.0, 1e-45, 1e-38, 3e38, 1.0, 0.0]]], device="cuda")
+  assert ops.select_topk(s, 4).cpu().tolist() == [[[1, 2, 3, 4]]]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_roco_and_keyformer_selection(ops, dtype):
+  B, S, H, k_keep = 2, 1024, 3, 128
+  q, k, v, er = O.make_inputs("keyformer", B, S, S, H, 128, dtype, seed=31)
+  qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+  out, ssum, ssq, idx = ops.roco(qd, kd, vd, k_keep=k_keep)
+  idx = idx.cpu().numpy()
+  assert np.array_equal(idx, O.roco_select(ssum.cpu().numpy(), ssq.cpu().numpy(), k_keep, S))
+  _, rs, rq = O.roco(q, k, v)
+  mean, _ = O.roco_stats(rs.numpy(), rq.numpy(), S)
+  O.check_index_sets(idx, O.roco_select(rs.numpy(), rq.numpy(), k_keep, S), mean, k_keep)
+  out, score, idx = ops.keyformer(qd, kd, vd, er.cuda(), tau=1.5, k_keep=S // 4)
+  idx = idx.cpu().numpy()
+  assert np.array_equal(idx, O.keyformer_select(score.cpu().numpy(), S // 4))
+  ref = O.keyformer(q, k, v, er, 1.5)[1].numpy()
+  O.check_index_sets(idx, O.keyformer_select(ref, S // 4), ref, S // 4)
+  no_timeouts(ops)
+
+
+# ------------------------------------------------------------------------------------------
+# determinism and error behaviour on the device
+# ------------------------------------------------------------------------------------------
+def test_bitwise_reproducible(ops):
+  q, k, v = O.make_inputs("roco", 2, 1536, 1536, 4, 128, torch.bfloat16, seed=77)
+  qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+  a = ops.roco(qd, kd, vd, k_keep=192)
+  b = ops.roco(qd, kd, vd, k_keep=192)
+  for x, y in zip(a, b):
+    assert torch.equal(x, y)
+  s1 = ops.sima_fwd(qd, kd, vd)
+  s2 = ops.sima_fwd(qd, kd, vd)
+  assert torch.equal(s1, s2)
+
+
+def test_errors_raise_and_leave_the_device_usable(ops):
+  from flashtensor_b200 import _lib
+  q = torch.zeros(1, 256, 2, 128, dtype=torch.float16, device="cuda")
+  with pytest.raises(_lib.AsukaError, match="BAD_SHAPE"):
+    ops.attn_fwd(q, q[:, :128], q[:, :128])               # causal with fewer keys than queries
+  with pytest.raises(_lib.AsukaError, match="BAD_DTYPE"):
+    ops.attn_fwd(q, q.bfloat16(), q)
+  with pytest.raises(_lib.AsukaError, match="BAD_ARGUMENT"):
+    ops.h2o(q, q, q, k_keep=250, recent=16)               # k_keep > S - recent
+  with pytest.raises(_lib.AsukaError, match="MISALIGNED"):
+    flat = torch.zeros(256 * 2 * 128 + 8, dtype=torch.float16, device="cuda")
+    ops.attn_fwd(flat[4:4 + 256 * 2 * 128].view(1, 256, 2, 128), q, q)
+  out = ops.attn_fwd(q, q, q)                             # still works afterwards
+  torch.cuda.synchronize()
+  assert torch.count_nonzero(out) == 0
+  no_timeouts(ops)
+
+
+# ------------------------------------------------------------------------------------------
+# (3) full benchmark sizes: size-independent properties
+# ------------------------------------------------------------------------------------------
+def test_full_size_h2o_properties(ops):
+  # configuration C2: B=1, H=32, S=4096, fp16, k = S/8 + 256 recent
+  B, S, H = 1, 4096, 32
+  g = torch.Generator(device="cuda").manual_seed(0)
+  q = torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.float16)
+  k = torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.float16)
+  v = torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.float16)
+  out, score, idx = ops.h2o(q, k, v, k_keep=S // 8, recent=256)
+  torch.cuda.synchronize()
+  # (a) a head's scores sum to the number of query rows
+  torch.testing.assert_close(score.sum(-1), torch.full((B, H), float(S), device="cuda"), rtol=1e-4, atol=0.05)
+  # (b) causality: the first 1024 rows equal the computation on the first 1024 tokens alone
+  out_p, score_p = ops.h2o(q[:, :1024], k[:, :1024], v[:, :1024])
+  assert torch.equal(out[:, :1024], out_p)
+  # (c) a constant V gives a constant output
+  vc = torch.full_like(v, 0.5)
+  oc = ops.attn_fwd(q, k, vc)
+  torch.testing.assert_close(oc.float(), torch.full_like(oc, 0.5).float(), rtol=0, atol=2e-3)
+  # (d) the first row attends to key 0 only
+  torch.testing.assert_close(out[:, 0].float(), v[:, 0].float(), rtol=0, atol=1e-3)
+  # (e) index sets: ascending, in range, the recent window present, exact on the kernel's scores
+  idx_np = idx.cpu().numpy()
+  assert np.all(np.diff(idx_np, axis=-1) > 0) and idx_np.min() >= 0 and idx_np.max() == S - 1
+  assert np.array_equal(idx_np[..., -256:], np.broadcast_to(np.arange(S - 256, S), (B, H, 256)))
+  assert np.array_equal(idx_np, O.h2o_select(score.cpu().numpy(), S // 8, 256))
+  # (f) one head against the oracle (the whole configuration takes the CPU ~10 s)
+  ref_out, ref_score = O.h2o(q[:, :, :1].cpu(), k[:, :, :1].cpu(), v[:, :, :1].cpu())
+  close(out[:, :, :1], ref_out, "C2 head 0 out")
+  close(score[:, :1], ref_score, "C2 head 0 score")
+  no_timeouts(ops)
+
+
+def test_full_size_roco_and_sima_properties(ops):
+  # RoCo at C4's sequence length and dtype (fewer heads: the property does not depend on them)
+  B, S, H = 2, 4096, 8
+  g = torch.Generator(device="cuda").manual_seed(1)
+  q, k, v = (torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+  out, ssum, ssq = ops.roco(q, k, v)
+  torch.testing.assert_close(ssum.sum(-1), torch.full((B, H), float(S), device="cuda"), rtol=1e-4, atol=0.05)
+  assert torch.all(ssq <= ssum * 1.0001 + 1e-6) and torch.all(ssq >= 0)
+  # key S-1 is seen by the last row only: sum = p, sumsq = p^2
+  torch.testing.assert_close(ssq[..., -1], ssum[..., -1] ** 2, rtol=1e-4, atol=1e-9)
+  # SimA at C5's sequence length: invariance to the scale of K and of Q, linearity in V
+  B, S, H = 1, 8192, 4
+  q, k = (torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.float16) for _ in range(2))
+  v = (torch.rand(B, S, H, 128, generator=g, device="cuda") * 2 - 1).half()
+  o = ops.sima_fwd(q, k, v, out_dtype=torch.float32)
+  scale = o.abs().max()
+  assert torch.equal(ops.sima_fwd(q, k * 2, v, out_dtype=torch.float32), o)      # exact: powers of two
+  assert torch.equal(ops.sima_fwd(q * 4, k, v, out_dtype=torch.float32), o)
+  torch.testing.assert_close(ops.sima_fwd(q, k, v * 2, out_dtype=torch.float32), 2 * o, rtol=0, atol=float(scale) * 1e-5)
+  # every L1-normalised channel of Q sums (in absolute value) to one: with K = sign pattern of
+  # ones and V = ones, out[s, e] = sum_d Qn[s, d]
+  ones = torch.ones_like(q)
+  o1 = ops.sima_fwd(q, ones, ones, out_dtype=torch.float32)
+  qn = q.float() / q.float().abs().sum(1, keepdim=True)
+  torch.testing.assert_close(o1, qn.sum(-1, keepdim=True).expand_as(o1), rtol=0, atol=float(o1.abs().max()) * 2e-3)
+  no_timeouts(ops)
