@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/asuka_b200.h"
 #include "kernels.h"
@@ -389,6 +390,30 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
   return r;
 }
 
+// ---- scratch for asuka_b200_h2o_static -------------------------------------------------------
+// The array lives in the library's device image: one copy per GPU that loads the library.
+// In HOST code the name `g_h2o_static_scratch` is only a handle for the runtime, not a device
+// address; the address a kernel can use comes from cudaGetSymbolAddress, asked once per device
+// with that device current.
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(ASUKA_H2O_STATIC_MAX_ROWS) * sizeof(float) * 2;
+static __device__ __align__(256) unsigned char g_h2o_static_scratch[kStaticScratchBytes];
+
+int h2o_static_scratch(void** out) {
+  static std::mutex mu;
+  static void* cache[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ASUKA_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_h2o_static_scratch);
+    if (e != cudaSuccess || p == nullptr) return ASUKA_ERR_CUDA;
+    cache[dev] = p;
+  }
+  *out = cache[dev];
+  return ASUKA_OK;
+}
+
 }  // namespace
 }  // namespace asuka
 
@@ -473,6 +498,23 @@ int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes) {
 
 int asuka_b200_h2o(const asuka_case_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
   return case_impl(p, CASE_H2O, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+// H2O with the row statistic in the library's own fixed device array: no workspace argument, no
+// allocation.  The size check comes first, so an oversized request never reaches a launch.  The
+// first call on a device resolves the array's address (see h2o_static_scratch above).
+int asuka_b200_h2o_static(const asuka_case_params* p, asuka_stream stream) {
+  if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (p->q.ndim != 4) return ASUKA_ERR_BAD_SHAPE;
+  for (int i = 0; i < 3; ++i)
+    if (p->q.shape[i] <= 0) return ASUKA_ERR_BAD_SHAPE;
+  const double rows = static_cast<double>(p->q.shape[0]) * static_cast<double>(p->q.shape[1]) *
+                      static_cast<double>(p->q.shape[2]);
+  if (rows > static_cast<double>(ASUKA_H2O_STATIC_MAX_ROWS) || case_ws_bytes(p) > kStaticScratchBytes)
+    return ASUKA_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int r = h2o_static_scratch(&scratch);
+  if (r != ASUKA_OK) return r;
+  return case_impl(p, CASE_H2O, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }
 int asuka_b200_roco(const asuka_case_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
   return case_impl(p, CASE_ROCO, ws, ws_bytes, static_cast<cudaStream_t>(stream));

@@ -178,6 +178,23 @@ def h2o(q, k, v, causal=True, softmax_scale=0.0, k_keep=0, recent=0, **buffers):
   return (out, score, idx) if n_idx else (out, score)
 
 
+def h2o_static(q, k, v, out, score, idx=None, causal=True, softmax_scale=0.0, k_keep=0, recent=0):
+  """H2O through the entry point that allocates nothing: the caller supplies every output
+  (`out`, `score`, optionally `idx`), and the scratch between the two kernels is the library's
+  fixed device array.  For hosts that may not allocate on the call path (engine plug-ins, fully
+  pre-reserved memory pools); limited to B*H*Sq <= 524288 rows, and calls on one device must not
+  overlap.  This wrapper itself creates no tensors."""
+  lib = _lib.load()
+  q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
+  _same_device(q4, k4, v4, out, score, idx)
+  with torch.cuda.device(q4.device):
+    p = _lib.CaseParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(score),
+                        _lib.Tensor(), _lib.Tensor(), _desc(idx), float(softmax_scale), 1.0, 0,
+                        int(bool(causal)), int(k_keep), int(recent))
+    _lib.check("asuka_b200_h2o_static", lib.asuka_b200_h2o_static(ctypes.byref(p), _stream(q4)))
+  return (out, score, idx) if idx is not None else (out, score)
+
+
 def roco(q, k, v, causal=True, softmax_scale=0.0, k_keep=0, **buffers):
   """(out, roco_score, roco_sq_score[, idx]) -- cases/kernels/roco.py:18-48."""
   out, score, sq, idx = _case("asuka_b200_roco", q, k, v, causal, softmax_scale, want_sq=True,

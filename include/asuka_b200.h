@@ -173,6 +173,32 @@ int asuka_b200_roco(const asuka_case_params* p, void* workspace, size_t workspac
 int asuka_b200_keyformer(const asuka_case_params* p, void* workspace, size_t workspace_bytes,
                          asuka_stream stream);
 
+/* ---- H2O for callers that can neither pass scratch memory nor let the library allocate.
+ *      This entry point has no counterpart in the reference, whose generated callables allocate
+ *      whatever they need with torch.empty.
+ *
+ * Who needs it: a plug-in hosted by an inference engine whose enqueue hook must not allocate; a
+ * serving process whose own memory pool already holds the whole device, so that a cudaMalloc made
+ * on its behalf simply fails; a latency-critical loop that cannot afford the device-wide
+ * synchronisation an allocation brings.  For them this variant of asuka_b200_h2o keeps the one
+ * piece of scratch the case needs -- the per-row softmax statistic handed from the forward kernel
+ * to the column-score kernel -- in a fixed array that is part of the library's device image.
+ * It calls no cudaMalloc, cudaFree or any allocating routine; inputs and outputs still come from
+ * the caller exactly as for asuka_b200_h2o (same parameter block, `idx` optional).
+ *
+ * Limits and rules:
+ *  - B * H * Sq must not exceed ASUKA_H2O_STATIC_MAX_ROWS; larger problems are refused with
+ *    ASUKA_ERR_TOO_LARGE before anything is launched (use asuka_b200_h2o with a workspace).
+ *  - The array (4 MiB) occupies memory on every GPU that loads the library, until the process exits.
+ *  - The first call on each device looks up the array's device address (the device must be current,
+ *    as for every call here) and remembers it.  Make that first call ahead of any stream capture.
+ *  - All calls on a device share the one array.  Nothing in it has to start at zero -- the forward
+ *    kernel rewrites every row it later reads -- but two calls whose kernels overlap on the GPU
+ *    (different streams, or different host threads) race on it: keep calls on a device in order.
+ */
+#define ASUKA_H2O_STATIC_MAX_ROWS 524288
+int asuka_b200_h2o_static(const asuka_case_params* p, asuka_stream stream);
+
 /* ---- library services ---- */
 int asuka_b200_version(void);
 const char* asuka_b200_strerror(int status);
