@@ -8,7 +8,8 @@
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong through the
 // tensor pipe so that the softmax of one overlaps the MMAs of the other.
-//   warp 0        TMA producer: Q once, then K/V tiles of 128 keys through a 2-stage ring
+//   warp 0        TMA producer: Q once, then K tiles of 128 keys through a 3-stage ring
+//   warp 2        TMA producer: V tiles through a 2-stage ring
 //   warp 1        issues tcgen05.mma: S_t = Q_t K^T (SMEM x SMEM), O_t += P_t V (TMEM x SMEM)
 //   warps 4-7     softmax of tile 0: one thread per query row, whole row of S in registers
 //   warps 8-11    softmax of tile 1
@@ -29,10 +30,14 @@ namespace {
 constexpr int kTile = 128;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;  // one [128 x 128] 16-bit tile = two swizzled halves
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
-constexpr int kStages = 2;
+constexpr int kKStages = 3;  // K(j) is needed one iteration before V(j): give it the deeper ring
+constexpr int kVStages = 2;
 constexpr int kThreads = 384;
-constexpr uint32_t kSmemBytes = (2 + 2 * kStages) * kTileBytes + 1024;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kUtilRegs = 96;      // 128 * 96 + 256 * 200 = 63488 <= 384 * 168
+constexpr int kSoftmaxRegs = 200;
+constexpr uint32_t kSmemBytes = (2 + kKStages + kVStages) * kTileBytes + 1024;
+constexpr float kRescaleLimit = 8192.0f;  // largest tile row sum tolerated under a stale reference:
+                                          // bounds every exponential far below fp16's 65504
 
 struct FwdParams {
   int B, H, Sq, Skv;
@@ -45,8 +50,8 @@ struct FwdParams {
 
 struct Bars {
   uint64_t q_full[2];
-  uint64_t k_full[kStages], k_empty[kStages];
-  uint64_t v_full[kStages], v_empty[kStages];
+  uint64_t k_full[kKStages], k_empty[kKStages];
+  uint64_t v_full[kVStages], v_empty[kVStages];
   uint64_t s_full[2], p_ready[2], o_done[2], epi[2];
 };
 
@@ -64,6 +69,15 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   } else {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <bool kBF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (kBF16) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  } else {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
   }
 }
 
@@ -96,8 +110,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base;                          // 2 tiles
-  const uint32_t sK = smem_base + 2 * kTileBytes;         // kStages tiles
-  const uint32_t sV = sK + kStages * kTileBytes;          // kStages tiles
+  const uint32_t sK = smem_base + 2 * kTileBytes;         // kKStages tiles
+  const uint32_t sV = sK + kKStages * kTileBytes;         // kVStages tiles
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -122,9 +136,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(smem_u32(&bars.o_done[i]), 1);
       mbar_init(smem_u32(&bars.epi[i]), 128);
     }
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < kKStages; ++i) {
       mbar_init(smem_u32(&bars.k_full[i]), 1);
       mbar_init(smem_u32(&bars.k_empty[i]), 1);
+    }
+    for (int i = 0; i < kVStages; ++i) {
       mbar_init(smem_u32(&bars.v_full[i]), 1);
       mbar_init(smem_u32(&bars.v_empty[i]), 1);
     }
@@ -144,8 +160,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
 
+  // 384 threads x 168 registers: the four utility warps hand most of theirs to the softmax warps
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    reg_dealloc<kUtilRegs>();
     if (lane == 0) {
       bool ok = true;
       for (int t = 0; t < 2; ++t) {
@@ -157,99 +175,133 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       int issued = 0;
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j % kStages;
-        const uint32_t use = static_cast<uint32_t>(j / kStages);
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % kKStages;
+        const uint32_t use = static_cast<uint32_t>(j / kKStages);
         if (use > 0) {
           ok = mbar_wait(smem_u32(&bars.k_empty[st]), (use - 1) & 1, abortp);
           if (!ok) { record_timeout(p.status, 1); break; }
         }
-        {
-          const uint32_t bar = smem_u32(&bars.k_full[st]);
-          mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, h, j * kTile, b);
-          tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
-        }
-        if (use > 0) {
-          ok = mbar_wait(smem_u32(&bars.v_empty[st]), (use - 1) & 1, abortp);
-          if (!ok) { record_timeout(p.status, 2); issued = j; break; }
-        }
-        {
-          const uint32_t bar = smem_u32(&bars.v_full[st]);
-          mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, h, j * kTile, b);
-          tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, h, j * kTile, b);
-        }
+        const uint32_t bar = smem_u32(&bars.k_full[st]);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, h, j * kTile, b);
+        tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
         issued = j + 1;
       }
       if (!ok) {
         // give copies already in flight a bounded chance to land before the CTA retires
         volatile uint32_t none = 0;
-        for (int j = max(0, issued - kStages); j < issued; ++j) {
-          mbar_wait(smem_u32(&bars.k_full[j % kStages]), (j / kStages) & 1, &none);
-          mbar_wait(smem_u32(&bars.v_full[j % kStages]), (j / kStages) & 1, &none);
+        for (int j = max(0, issued - kKStages); j < issued; ++j)
+          mbar_wait(smem_u32(&bars.k_full[j % kKStages]), (j / kKStages) & 1, &none);
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ TMA producer for V
+    reg_dealloc<kUtilRegs>();
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % kVStages;
+        const uint32_t use = static_cast<uint32_t>(j / kVStages);
+        if (use > 0) {
+          ok = mbar_wait(smem_u32(&bars.v_empty[st]), (use - 1) & 1, abortp);
+          if (!ok) { record_timeout(p.status, 2); break; }
         }
+        const uint32_t bar = smem_u32(&bars.v_full[st]);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, h, j * kTile, b);
+        tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, h, j * kTile, b);
+        issued = j + 1;
+      }
+      if (!ok) {
+        volatile uint32_t none = 0;
+        for (int j = max(0, issued - kVStages); j < issued; ++j)
+          mbar_wait(smem_u32(&bars.v_full[j % kVStages]), (j / kVStages) & 1, &none);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // One warp issues for both tiles, in the order P.V_0(j-1), QK_0(j), P.V_1(j-1), QK_1(j): the
+    // S/P aliasing of a tile is ordered by program order, and the two tiles are forced to
+    // alternate (their softmax phases share the MUFU, so they must not run in step).  The whole
+    // warp walks the loop (addresses and descriptors stay warp-uniform, waits are converged); one
+    // elected lane issues the tcgen05.mma / commit instructions.  Barriers that are normally
+    // already complete are probed together so that their latencies overlap.
+    reg_dealloc<kUtilRegs>();
+    {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
       constexpr uint32_t idesc_qk = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_MN_MAJOR, 128, 128);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t site) -> bool {
+        const bool good = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, abortp));
+        if (!good && lane == 0) record_timeout(p.status, site);
+        return good;
+      };
       bool ok = true;
       for (int t = 0; t < 2 && ok; ++t) {
-        if (n_kv[t] > 0) {
-          ok = mbar_wait(smem_u32(&bars.q_full[t]), 0, abortp);
-          if (!ok) record_timeout(p.status, 3);
-        }
+        if (n_kv[t] > 0) ok = wait_all(&bars.q_full[t], 0, 3);
       }
       for (int j = 0; j <= n_max && ok; ++j) {
-        const int st = j % kStages;
-        if (j < n_max) {
-          ok = mbar_wait(smem_u32(&bars.k_full[st]), (j / kStages) & 1, abortp);
-          if (!ok) { record_timeout(p.status, 4); break; }
-        }
+        const int st = j % kKStages;
         const int jp = j - 1;  // the tile whose P.V is issued in this iteration
-        const int stp = (jp + kStages) % kStages;
-        if (jp >= 0) {
-          ok = mbar_wait(smem_u32(&bars.v_full[stp]), (jp / kStages) & 1, abortp);
-          if (!ok) { record_timeout(p.status, 5); break; }
-        }
-        tc_fence_after_sync();
-        for (int t = 0; t < 2 && ok; ++t) {
+        const int stp = (jp + kVStages) % kVStages;
+        const bool have_k = j < n_max, have_v = jp >= 0;
+        const bool pv0 = have_v && jp < n_kv[0], pv1 = have_v && jp < n_kv[1];
+        // probe everything this iteration needs at once; fall back to a proper wait on a miss
+        const bool k_hit = !have_k || mbar_try_wait(smem_u32(&bars.k_full[st]), (j / kKStages) & 1);
+        const bool v_hit = !have_v || mbar_try_wait(smem_u32(&bars.v_full[stp]), (jp / kVStages) & 1);
+        const bool p0_hit = !pv0 || mbar_try_wait(smem_u32(&bars.p_ready[0]), jp & 1);
+        if (!__all_sync(0xffffffffu, k_hit)) ok = wait_all(&bars.k_full[st], (j / kKStages) & 1, 4);
+        if (ok && !__all_sync(0xffffffffu, v_hit)) ok = wait_all(&bars.v_full[stp], (jp / kVStages) & 1, 5);
+        if (!ok) break;
+        const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
+        const uint64_t vdesc = umma_smem_desc_sw128(sV + stp * kTileBytes, kHalfBytes, 1024);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
           const uint32_t tS = tbase + t * 128;          // S_t, and P_t in its first 64 columns
           const uint32_t tO = tbase + 256 + t * 128;    // O_t
-          if (jp >= 0 && jp < n_kv[t]) {
-            ok = mbar_wait(smem_u32(&bars.p_ready[t]), jp & 1, abortp);
-            if (!ok) { record_timeout(p.status, 6); break; }
-            tc_fence_after_sync();
-            const uint64_t vdesc = umma_smem_desc_sw128(sV + stp * kTileBytes, kHalfBytes, 1024);
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-              umma_ts(tO, tS + kk * 8, vdesc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
-                      (jp > 0 || kk > 0) ? 1u : 0u);
+          const bool pv = t == 0 ? pv0 : pv1;
+          const bool qk = j < n_kv[t];
+          if (pv) {
+            if (t == 1 || !__all_sync(0xffffffffu, p0_hit)) {
+              ok = wait_all(&bars.p_ready[t], jp & 1, 6);
+              if (!ok) break;
             }
-            umma_commit(smem_u32(&bars.o_done[t]));
           }
-          if (j < n_kv[t]) {
-            const uint64_t qdesc = umma_smem_desc_sw128(sQ + t * kTileBytes, 16, 1024);
-            const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
+          tc_fence_after_sync();
+          if (elect_one()) {
+            if (pv) {
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-              const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
-              umma_ss(tS, qdesc + off, kdesc + off, idesc_qk, kk > 0 ? 1u : 0u);
+              for (int kk = 0; kk < 8; ++kk) {
+                umma_ts(tO, tS + kk * 8, vdesc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
+                        (jp > 0 || kk > 0) ? 1u : 0u);
+              }
+              // O_t is complete after its last P.V; the V stage is free after tile 1's P.V
+              if (jp == n_kv[t] - 1) umma_commit(smem_u32(&bars.o_done[t]));
+              if (t == 1 || !pv1) umma_commit(smem_u32(&bars.v_empty[stp]));
             }
-            umma_commit(smem_u32(&bars.s_full[t]));
+            if (qk) {
+              const uint64_t qdesc = umma_smem_desc_sw128(sQ + t * kTileBytes, 16, 1024);
+#pragma unroll
+              for (int kk = 0; kk < 8; ++kk) {
+                const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+                umma_ss(tS, qdesc + off, kdesc + off, idesc_qk, kk > 0 ? 1u : 0u);
+              }
+              umma_commit(smem_u32(&bars.s_full[t]));
+            }
+            // the K stage is free after the last QK^T that reads it
+            if (qk && (t == 1 || j >= n_kv[1])) umma_commit(smem_u32(&bars.k_empty[st]));
           }
+          __syncwarp();
         }
-        if (!ok) break;
-        if (j < n_max) umma_commit(smem_u32(&bars.k_empty[st]));
-        if (jp >= 0) umma_commit(smem_u32(&bars.v_empty[stp]));
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    reg_dealloc<kUtilRegs>();
+  } else {
     // ------------------------------------------------------------------ softmax + epilogue
+    reg_alloc<kSoftmaxRegs>();
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;                     // TMEM lane quarter this warp may touch
     const int r_in_tile = wq * 32 + lane;
@@ -263,46 +315,76 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (p.causal) lim = min(lim, row + p.diag_off);
     const int tile_min_lim = p.causal ? min(p.Skv - 1, q0[t] + p.diag_off) : p.Skv - 1;
 
-    float m_ref = -INFINITY;
-    float l = 0.f;
+    float m_ref = -INFINITY;             // exponent reference of this row (raw logit units)
+    float l = 0.f;                       // row sum under the current reference
     bool ok = true;
 
-    for (int j = 0; j < n_t; ++j) {
+    for (int j = 0; j < n_t && ok; ++j) {
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[t]), j & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 7); break; }
       tc_fence_after_sync();
-      float s[128];
+      const bool masked_tile = j * kTile + kTile - 1 > tile_min_lim;
+      const int thr = lim - j * kTile;  // columns > thr of this tile are masked for this row
+
+      // The whole 128-wide row is exponentiated at once against the reference left by earlier
+      // tiles, so the MUFU starts right after the TMEM load and runs without a gap; the largest
+      // result is looked at afterwards.  If it exceeds 2^8 -- or is not finite, as in the very
+      // first tile, which has no reference yet -- the rare path takes the true maximum, moves the
+      // reference up, rescales what was accumulated under the old one and redoes the tile.
+      float e[128];
       {
-        uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(s);
+        uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(e);
         tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
         tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
         tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&u[64]));
         tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&u[96]));
         tmem_wait_ld();
       }
-      if (j * kTile + kTile - 1 > tile_min_lim) {
-        const int thr = lim - j * kTile;
+      if (masked_tile) {
 #pragma unroll
-        for (int c = 0; c < 128; ++c) s[c] = (c > thr) ? -INFINITY : s[c];
+        for (int i = 0; i < 128; ++i) e[i] = (i > thr) ? -INFINITY : e[i];
       }
-      float m_tile = s[0];
+      {
+        const float neg_m = -m_ref * scale;
 #pragma unroll
-      for (int c = 1; c < 128; ++c) m_tile = fmaxf(m_tile, s[c]);
-      const float m_new = fmaxf(m_ref, m_tile);
-      if (j == 0) {
-        m_ref = m_new;
-      } else {
-        const bool need = (m_new - m_ref) * scale > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), (j - 1) & 1, abortp));
-          if (!ok) { if (lane == 0) record_timeout(p.status, 8); break; }
-          tc_fence_after_sync();
-          float alpha = 1.f;
-          if (need) {
-            alpha = ex2((m_ref - m_new) * scale);
-            m_ref = m_new;
-            l *= alpha;
+        for (int i = 0; i < 128; ++i) e[i] = ex2(fmaf(e[i], scale, neg_m));
+      }
+      // The tile's row sum doubles as the overflow probe: it bounds every term from above, and it
+      // is NaN or infinite exactly when some term is (first tile: no reference yet).  P is packed
+      // to 16 bits right away (the compiler interleaves it with the exponentials), so that only
+      // the TMEM store is left once the probe has passed.
+      float ts8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        ts8[i & 7] += e[2 * i] + e[2 * i + 1];
+        pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
+      }
+      float tile_sum = ((ts8[0] + ts8[1]) + (ts8[2] + ts8[3])) + ((ts8[4] + ts8[5]) + (ts8[6] + ts8[7]));
+      const bool need = !(tile_sum <= kRescaleLimit);
+      if (__any_sync(0xffffffffu, need)) {
+        // ---- rare: the raw logits are still intact in TMEM; take their maximum, 32 columns at a time
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t u[32];
+          tmem_ld32(tS + c * 32, u);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
+            mx = fmaxf(mx, v);
           }
+        }
+        float alpha = 1.f;
+        if (need) {
+          alpha = ex2((m_ref - mx) * scale);  // 0 when there was no reference yet
+          m_ref = mx;
+          l *= alpha;
+        }
+        if (j > 0) {
+          // O_t is the sum over earlier tiles.  P.V of tile j-1 was issued before QK^T of tile j
+          // and the tensor pipe retires in order, so S_t(j) being ready means O_t is complete.
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
@@ -314,28 +396,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           tmem_wait_st();
         }
-      }
-      const float neg_m = -m_ref * scale;
+        const float neg_m = -m_ref * scale;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t u[32];
+          tmem_ld32(tS + c * 32, u);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(s[c * 32 + 2 * i], scale, neg_m));
-          const float p1 = ex2(fmaf(s[c * 32 + 2 * i + 1], scale, neg_m));
-          l += p0;
-          l += p1;
-          pk[i] = pack2<kBF16>(p0, p1);
+          for (int i = 0; i < 32; ++i) {
+            const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
+            e[c * 32 + i] = ex2(fmaf(v, scale, neg_m));
+          }
         }
-        tmem_st16(tS + c * 16, pk);
+        tile_sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          tile_sum += e[2 * i] + e[2 * i + 1];
+          pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
+        }
       }
+      l += tile_sum;
+      tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+      tmem_st32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+      if (!ok) break;
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bars.p_ready[t]));
     }
 
     if (ok && n_t > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), (n_t - 1) & 1, abortp));
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), 0, abortp));  // committed once, after the last P.V
       if (!ok && lane == 0) record_timeout(p.status, 9);
     }
     if (ok && n_t > 0) {

@@ -172,38 +172,49 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (warp-uniform descriptors, converged waits); one elected lane
+    // issues the tcgen05.mma / commit instructions.
+    {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
-      bool ok = mbar_wait(smem_u32(&bars.k_full), 0, abortp);
-      if (!ok) record_timeout(p.status, 22);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t site) -> bool {
+        const bool good = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, abortp));
+        if (!good && lane == 0) record_timeout(p.status, site);
+        return good;
+      };
+      bool ok = wait_all(&bars.k_full, 0, 22);
       for (int i = i_begin; i < p.nq_tiles && ok; ++i) {
         const int c = i - i_begin;
         const int st = c % kQStages;
-        ok = mbar_wait(smem_u32(&bars.q_full[st]), (c / kQStages) & 1, abortp);
-        if (!ok) { record_timeout(p.status, 23); break; }
+        ok = wait_all(&bars.q_full[st], (c / kQStages) & 1, 23);
+        if (!ok) break;
         tc_fence_after_sync();
         const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
+#pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (!active[t] || i < i_start[t]) continue;
           const int ct = i - i_start[t];
           const int buf = ct & 1;
           if (ct >= 2) {
-            ok = mbar_wait(smem_u32(&bars.s_empty[t][buf]), ((ct >> 1) - 1) & 1, abortp);
-            if (!ok) { record_timeout(p.status, 24); break; }
+            ok = wait_all(&bars.s_empty[t][buf], ((ct >> 1) - 1) & 1, 24);
+            if (!ok) break;
             tc_fence_after_sync();
           }
           const uint64_t kdesc = umma_smem_desc_sw128(sK + t * kTileBytes, 16, 1024);
           const uint32_t tS = tbase + (t * 2 + buf) * 128;
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
-            umma_ss(tS, kdesc + off, qdesc + off, idesc, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+              umma_ss(tS, kdesc + off, qdesc + off, idesc, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&bars.s_full[t][buf]));
           }
-          umma_commit(smem_u32(&bars.s_full[t][buf]));
+          __syncwarp();
         }
         if (!ok) break;
-        umma_commit(smem_u32(&bars.q_empty[st]));
+        if (elect_one()) umma_commit(smem_u32(&bars.q_empty[st]));
+        __syncwarp();
       }
     }
   } else if (warp >= 4) {
@@ -375,29 +386,36 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
-      bool ok = mbar_wait(smem_u32(&bars.q_full), 0, abortp);
-      if (!ok) record_timeout(p.status, 32);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t site) -> bool {
+        const bool good = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, abortp));
+        if (!good && lane == 0) record_timeout(p.status, site);
+        return good;
+      };
+      bool ok = wait_all(&bars.q_full, 0, 32);
       const uint64_t qdesc = umma_smem_desc_sw128(sQ, 16, 1024);
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j % kRsStages, buf = j & 1;
-        ok = mbar_wait(smem_u32(&bars.k_full[st]), (j / kRsStages) & 1, abortp);
-        if (!ok) { record_timeout(p.status, 33); break; }
+        ok = wait_all(&bars.k_full[st], (j / kRsStages) & 1, 33);
+        if (!ok) break;
         if (j >= 2) {
-          ok = mbar_wait(smem_u32(&bars.s_empty[buf]), ((j >> 1) - 1) & 1, abortp);
-          if (!ok) { record_timeout(p.status, 34); break; }
+          ok = wait_all(&bars.s_empty[buf], ((j >> 1) - 1) & 1, 34);
+          if (!ok) break;
         }
         tc_fence_after_sync();
         const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
-          umma_ss(tbase + buf * 128, qdesc + off, kdesc + off, idesc, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+            umma_ss(tbase + buf * 128, qdesc + off, kdesc + off, idesc, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars.s_full[buf]));
+          umma_commit(smem_u32(&bars.k_empty[st]));
         }
-        umma_commit(smem_u32(&bars.s_full[buf]));
-        umma_commit(smem_u32(&bars.k_empty[st]));
+        __syncwarp();
       }
     }
   } else {

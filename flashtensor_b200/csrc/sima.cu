@@ -140,27 +140,32 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // whole warp walks the loop; one elected lane issues the MMAs
+    {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_MN_MAJOR, UMMA_MN_MAJOR, 128, 128);
       bool ok = true;
       for (int i = 0; i < ntile && ok; ++i) {
         const int st = i % kStStages;
-        ok = mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp);
-        if (!ok) { record_timeout(p.status, 42); break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp));
+        if (!ok) { if (lane == 0) record_timeout(p.status, 42); break; }
         tc_fence_after_sync();
         const uint32_t base = smem_base + st * 3 * kTileBytes;
         // M = K^T V: TMEM lane = d, column = e
         const uint64_t adesc = umma_smem_desc_sw128(base, kHalfBytes, 1024);               // K
         const uint64_t bdesc = umma_smem_desc_sw128(base + kTileBytes, kHalfBytes, 1024);  // V
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t off = static_cast<uint64_t>(kk * (2048 >> 4));
-          umma_ss(tbase, adesc + off, bdesc + off, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = static_cast<uint64_t>(kk * (2048 >> 4));
+            umma_ss(tbase, adesc + off, bdesc + off, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars.empty[st]));
         }
-        umma_commit(smem_u32(&bars.empty[st]));
+        __syncwarp();
       }
-      if (ok) umma_commit(smem_u32(&bars.m_done));
+      if (ok && elect_one()) umma_commit(smem_u32(&bars.m_done));
+      __syncwarp();
     }
   } else if (warp >= 4) {
     // warps 4-7: |K| column sums; warps 8-11: |Q| column sums
@@ -384,29 +389,36 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && ntile > 0) {
+    if (ntile > 0) {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
-      bool ok = mbar_wait(smem_u32(&bars.m_full), 0, abortp);
-      if (!ok) record_timeout(p.status, 52);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t site) -> bool {
+        const bool good = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, abortp));
+        if (!good && lane == 0) record_timeout(p.status, site);
+        return good;
+      };
+      bool ok = wait_all(&bars.m_full, 0, 52);
       const uint64_t mdesc = umma_smem_desc_sw128(sM, 16, 1024);
       for (int i = 0; i < ntile && ok; ++i) {
         const int st = i % kOutStages, buf = i & 1;
-        ok = mbar_wait(smem_u32(&bars.q_full[st]), (i / kOutStages) & 1, abortp);
-        if (!ok) { record_timeout(p.status, 53); break; }
+        ok = wait_all(&bars.q_full[st], (i / kOutStages) & 1, 53);
+        if (!ok) break;
         if (i >= 2) {
-          ok = mbar_wait(smem_u32(&bars.acc_empty[buf]), ((i >> 1) - 1) & 1, abortp);
-          if (!ok) { record_timeout(p.status, 54); break; }
+          ok = wait_all(&bars.acc_empty[buf], ((i >> 1) - 1) & 1, 54);
+          if (!ok) break;
         }
         tc_fence_after_sync();
         const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
-          umma_ss(tbase + buf * 128, qdesc + off, mdesc + off, idesc, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+            umma_ss(tbase + buf * 128, qdesc + off, mdesc + off, idesc, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars.acc_full[buf]));
+          umma_commit(smem_u32(&bars.q_empty[st]));
         }
-        umma_commit(smem_u32(&bars.acc_full[buf]));
-        umma_commit(smem_u32(&bars.q_empty[st]));
+        __syncwarp();
       }
     }
   } else if (warp >= 4) {

@@ -139,6 +139,25 @@ def test_sima_vs_oracle(ops, shape, dtype):
   no_timeouts(ops)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("direction", [1.0, -1.0])
+def test_logits_that_keep_growing_or_shrinking(ops, dtype, direction):
+  # keys scaled by a ramp along the sequence: the running maximum of a row keeps moving (or the
+  # first tile dominates everything after it), which drives the kernel's exponent-reference
+  # update and its rescaling of O and of the row sum
+  for (B, Sq, Skv, H, causal) in [(1, 384, 384, 2, True), (1, 200, 456, 2, True), (1, 300, 300, 1, False),
+                                  (2, 1024, 1024, 2, True)]:
+    q, k, v = O.make_inputs("h2o", B, Sq, Skv, H, 128, dtype, seed=3)
+    ramp = direction * (1 + torch.arange(Skv).float() / 16).view(1, Skv, 1, 1)
+    k = (k.float() * ramp).to(dtype)
+    ref_out, ref_score = O.h2o(q, k, v, causal)
+    out, score = ops.h2o(q.cuda(), k.cuda(), v.cuda(), causal=causal)
+    torch.cuda.synchronize()
+    close(out, ref_out, "out")
+    close(score, ref_score, "score")
+  no_timeouts(ops)
+
+
 def test_layouts_strided_and_2d(ops):
   # heads sliced out of a larger buffer (non-contiguous), and the 2-D [S, H*D] layout of cases/attn.py
   B, S, H = 2, 256, 4
