@@ -34,6 +34,8 @@ constexpr uint32_t kTileBytes = 128 * 128 * 2;
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
 constexpr int kQStages = 4;
 constexpr int kThreads = 384;
+constexpr int kColUtilRegs = 96;   // 128 * 96 + 256 * 200 <= 384 * 168
+constexpr int kColKeyRegs = 200;
 constexpr uint32_t kSmemBytes = (2 + kQStages) * kTileBytes + 1024;
 
 struct ColParams {
@@ -130,8 +132,10 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
 
+  // 384 threads x 168 registers: the utility warps hand registers to the per-key warps
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (whole warp)
+    reg_dealloc<kColUtilRegs>();
     if (lane == 0) {
       const uint32_t bar = smem_u32(&bars.k_full);
       mbar_expect_tx(bar, kTileBytes * n_active);
@@ -174,6 +178,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     // The whole warp walks the loop (warp-uniform descriptors, converged waits); one elected lane
     // issues the tcgen05.mma / commit instructions.
+    reg_dealloc<kColUtilRegs>();
     {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
@@ -217,8 +222,11 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         __syncwarp();
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    reg_dealloc<kColUtilRegs>();
+  } else {
     // ------------------------------------------------------------------ one thread per key
+    reg_alloc<kColKeyRegs>();
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;
     const int key = kv0[t] + wq * 32 + lane;
@@ -247,41 +255,58 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           if (!ok) { if (lane == 0) record_timeout(p.status, 26); break; }
           tc_fence_after_sync();
           const uint32_t tS = tbase + lane_base + (t * 2 + buf) * 128;
-          float s[128];
-          {
-            uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(s);
-            tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
-            tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
-            tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&u[64]));
-            tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&u[96]));
-            tmem_wait_ld();
-          }
-          tc_fence_before_sync();
-          mbar_arrive(smem_u32(&bars.s_empty[t][buf]));
-
           // query c of this tile sees `key` iff key <= (i*128 + c) + diag_off
           const int first_visible = p.causal ? key - p.diag_off - i * kTile : 0;
           const bool tile_has_mask = p.causal && (kv0[t] + kTile - 1 - p.diag_off > i * kTile);
           const float4* lse4 = reinterpret_cast<const float4*>(lse_s[st]);
+          // two halves of 64 queries: short enough that every exponential of a half is in flight
+          // at once without crowding the register file
 #pragma unroll
-          for (int g = 0; g < 32; ++g) {
-            const float4 L = lse4[g];
-            const float lv[4] = {L.x, L.y, L.z, L.w};
+          for (int hc = 0; hc < 2; ++hc) {
+            float s[64];
+            {
+              uint32_t(&u)[64] = *reinterpret_cast<uint32_t(*)[64]>(s);
+              tmem_ld32(tS + hc * 64, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
+              tmem_ld32(tS + hc * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
+            }
+            float noise[kMode == 2 ? 64 : 1];
+            if constexpr (kMode == 2) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int cc = g * 4 + e;
-              float x;
-              if constexpr (kMode == 2) {
-                const int qi = min(i * kTile + cc, p.Sq - 1);
-                const float er = __ldg(er_col + static_cast<int64_t>(qi) * p.er_sq);
-                x = fmaf(s[cc], scale, fmaf(lg2(er), -p.inv_tau, -lv[e]));
-              } else {
-                x = fmaf(s[cc], scale, -lv[e]);
+              for (int e = 0; e < 64; ++e) {
+                const int qi = min(i * kTile + hc * 64 + e, p.Sq - 1);
+                noise[e] = __ldg(er_col + static_cast<int64_t>(qi) * p.er_sq);
               }
-              float pv = ex2(x);
-              if (tile_has_mask) pv = (cc < first_visible) ? 0.f : pv;
-              acc[e] += pv;
-              if constexpr (kMode == 1) acc2[e] = fmaf(pv, pv, acc2[e]);
+            }
+            tmem_wait_ld();
+            if (hc == 1) {
+              // the whole tile is in registers: the MMA warp may overwrite this TMEM buffer
+              tc_fence_before_sync();
+              mbar_arrive(smem_u32(&bars.s_empty[t][buf]));
+            }
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+              const float4 L = lse4[hc * 16 + g];
+              const float lv[4] = {L.x, L.y, L.z, L.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int cc = g * 4 + e;
+                float x;
+                if constexpr (kMode == 2) {
+                  x = fmaf(s[cc], scale, fmaf(lg2(noise[cc]), -p.inv_tau, -lv[e]));
+                } else {
+                  x = fmaf(s[cc], scale, -lv[e]);
+                }
+                s[cc] = ex2(x);
+              }
+            }
+            if (tile_has_mask) {
+#pragma unroll
+              for (int cc = 0; cc < 64; ++cc) s[cc] = (hc * 64 + cc < first_visible) ? 0.f : s[cc];
+            }
+#pragma unroll
+            for (int cc = 0; cc < 64; ++cc) {
+              acc[cc & 3] += s[cc];
+              if constexpr (kMode == 1) acc2[cc & 3] = fmaf(s[cc], s[cc], acc2[cc & 3]);
             }
           }
         }
