@@ -23,6 +23,7 @@
 #include "../../include/asuka_b200.h"
 #include "kernels.h"
 #include "sm100_ptx.cuh"
+#include "tma_host.h"
 
 namespace asuka {
 using namespace sm100;
@@ -332,28 +333,39 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // ---------------------------------------------------------------------------------------------
 // Keyformer row pass: lse2'[row] = log2 sum_j exp2(((s_ij*scale + g_ij)/tau) * log2e)
 // One CTA per 128 query rows; one thread per row; K tiles stream through a ring.
+// kNoiseTma: the [128 x 128] f32 noise tile of every step is staged in shared memory by TMA
+// (four 128-byte-swizzled boxes of 32 keys) -- the kernel is bound by that 2 GB read, and a
+// thread walking its own row in global memory wastes most of every sector.  The plain variant
+// (direct loads) serves noise tensors whose strides TMA cannot describe.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRsStages = 4;
 constexpr int kRsThreads = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 rows
-constexpr uint32_t kRsSmemBytes = (1 + kRsStages) * kTileBytes + 1024;
+constexpr uint32_t kNoiseTileBytes = 128 * 128 * 4;
+template <bool kNoiseTma> struct RsCfg {
+  static constexpr int kStages = kNoiseTma ? 2 : 4;
+  static constexpr uint32_t kStageBytes = kTileBytes + (kNoiseTma ? kNoiseTileBytes : 0);
+  static constexpr uint32_t kSmem = kTileBytes + kStages * kStageBytes + 1024;
+};
 
 struct RsBars {
   uint64_t q_full;
-  uint64_t k_full[kRsStages], k_empty[kRsStages];
+  uint64_t k_full[4], k_empty[4];
   uint64_t s_full[2], s_empty[2];
 };
 
-template <bool kBF16>
+template <bool kBF16, bool kNoiseTma>
 __global__ void __launch_bounds__(kRsThreads, 1)
 kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const ColParams p, float* lse_out) {
+                  const __grid_constant__ CUtensorMap map_n, const ColParams p, float* lse_out) {
+  using Cfg = RsCfg<kNoiseTma>;
+  constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) RsBars bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base;
-  const uint32_t sK = smem_base + kTileBytes;
+  const uint32_t sStage = smem_base + kTileBytes;  // per stage: K tile, then (TMA variant) the noise tile
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile uint32_t* abortp = &abort_s;
@@ -369,9 +381,10 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (tid == 0) {
     abort_s = 0;
     mbar_init(smem_u32(&bars.q_full), 1);
-    for (int i = 0; i < kRsStages; ++i) {
+    for (int i = 0; i < kStages; ++i) {
       mbar_init(smem_u32(&bars.k_full[i]), 1);
-      mbar_init(smem_u32(&bars.k_empty[i]), 1);
+      // the MMA commit, plus (TMA variant) one arrival per row warp once the noise has been read
+      mbar_init(smem_u32(&bars.k_empty[i]), kNoiseTma ? 5 : 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars.s_full[i]), 1);
@@ -398,16 +411,23 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tma_load_4d(sQ + kHalfBytes, &map_q, bar, 64, h, q0, b);
       }
       for (int j = 0; j < n_kv; ++j) {
-        const int st = j % kRsStages;
-        const uint32_t use = static_cast<uint32_t>(j / kRsStages);
+        const int st = j % kStages;
+        const uint32_t use = static_cast<uint32_t>(j / kStages);
         if (use > 0 && !mbar_wait(smem_u32(&bars.k_empty[st]), (use - 1) & 1, abortp)) {
           record_timeout(p.status, 31);
           break;
         }
         const uint32_t bar = smem_u32(&bars.k_full[st]);
-        mbar_expect_tx(bar, kTileBytes);
-        tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, h, j * kTile, b);
-        tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
+        const uint32_t base = sStage + st * Cfg::kStageBytes;
+        mbar_expect_tx(bar, Cfg::kStageBytes);
+        tma_load_4d(base, &map_k, bar, 0, h, j * kTile, b);
+        tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
+        if constexpr (kNoiseTma) {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4)
+            tma_load_4d(base + kTileBytes + c4 * (kNoiseTileBytes / 4), &map_n, bar, j * kTile + c4 * 32, q0,
+                        h, b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -422,15 +442,15 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       bool ok = wait_all(&bars.q_full, 0, 32);
       const uint64_t qdesc = umma_smem_desc_sw128(sQ, 16, 1024);
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j % kRsStages, buf = j & 1;
-        ok = wait_all(&bars.k_full[st], (j / kRsStages) & 1, 33);
+        const int st = j % kStages, buf = j & 1;
+        ok = wait_all(&bars.k_full[st], (j / kStages) & 1, 33);
         if (!ok) break;
         if (j >= 2) {
           ok = wait_all(&bars.s_empty[buf], ((j >> 1) - 1) & 1, 34);
           if (!ok) break;
         }
         tc_fence_after_sync();
-        const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
+        const uint64_t kdesc = umma_smem_desc_sw128(sStage + st * Cfg::kStageBytes, 16, 1024);
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -445,7 +465,8 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
   } else {
     const int wq = warp & 3;  // warps 2,3,4,5 -> lane quarters 2,3,0,1
-    const int row = q0 + wq * 32 + lane;
+    const int r_in_tile = wq * 32 + lane;
+    const int row = q0 + r_in_tile;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     int lim = p.Skv - 1;
     if (p.causal) lim = min(lim, row + p.diag_off);
@@ -457,36 +478,54 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int buf = j & 1;
+      const int st = j % kStages;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[buf]), (j >> 1) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 35); break; }
       tc_fence_after_sync();
       const int thr = lim - j * kTile;  // columns > thr are masked
+      const uint8_t* noise_tile = smem_gen + kTileBytes + st * Cfg::kStageBytes + kTileBytes;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t u[32];
         tmem_ld32(tbase + lane_base + buf * 128 + c4 * 32, u);
+        float er[32];
+        if constexpr (kNoiseTma) {
+          // this row's 32 noise values of box c4: eight swizzled 16-byte chunks
+          const uint8_t* box = noise_tile + c4 * (kNoiseTileBytes / 4);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const float4 v = *reinterpret_cast<const float4*>(box + sw128_offset(r_in_tile, ch));
+            er[ch * 4 + 0] = v.x; er[ch * 4 + 1] = v.y; er[ch * 4 + 2] = v.z; er[ch * 4 + 3] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) er[e] = __ldg(er_row + min(j * kTile + c4 * 32 + e, p.Skv - 1));
+        }
         tmem_wait_ld();
         float x[32];
-        float mt = -INFINITY;
+        float mt4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int cc = c4 * 32 + e;
-          const int kj = min(j * kTile + cc, p.Skv - 1);
-          const float er = __ldg(er_row + kj);
-          const float v = fmaf(__uint_as_float(u[e]), scale, -lg2(er) * p.inv_tau);
+          const float v = fmaf(__uint_as_float(u[e]), scale, -lg2(er[e]) * p.inv_tau);
           x[e] = (cc > thr) ? -INFINITY : v;
-          mt = fmaxf(mt, x[e]);
+          mt4[e & 3] = fmaxf(mt4[e & 3], x[e]);
         }
-        const float m_new = fmaxf(m, mt);
+        const float m_new = fmaxf(m, fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3])));
         if (m_new > -INFINITY) {
-          l *= ex2(m - m_new);
+          float l4[4] = {l * ex2(m - m_new), 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int e = 0; e < 32; ++e) l += ex2(x[e] - m_new);
+          for (int e = 0; e < 32; ++e) l4[e & 3] += ex2(x[e] - m_new);
+          l = (l4[0] + l4[1]) + (l4[2] + l4[3]);
           m = m_new;
         }
       }
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bars.s_empty[buf]));
+      if constexpr (kNoiseTma) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.k_empty[st]));
+      }
     }
     if (ok && row < p.Sq) lse_out[(static_cast<size_t>(b) * p.H + h) * p.Sq + row] = m + log2f(l);
   }
@@ -548,10 +587,29 @@ cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, cons
                               float* lse2_out, const AttnShape& s, cudaStream_t stream) {
   const ColParams p = make_params(a, s);
   const dim3 grid(static_cast<unsigned>(p.nq_tiles) * s.B * s.H);
-  auto kern = s.bf16 ? kf_rowstat_kernel<true> : kf_rowstat_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kRsSmemBytes);
-  if (e != cudaSuccess) return e;
-  kern<<<grid, kRsThreads, kRsSmemBytes, stream>>>(mq, mk, p, lse2_out);
+  // TMA needs a 16-byte aligned base and strides that are multiples of 16 bytes
+  const bool tma_ok = (reinterpret_cast<uintptr_t>(a.exp_rand) & 15u) == 0 && a.er_stride_q % 4 == 0 &&
+                      a.er_stride_h % 4 == 0 && a.er_stride_b % 4 == 0 && a.er_stride_q > 0 &&
+                      a.er_stride_h > 0 && a.er_stride_b > 0;
+  cudaError_t e;
+  if (tma_ok) {
+    CUtensorMap mn;
+    const uint64_t dims[4] = {static_cast<uint64_t>(s.Skv), static_cast<uint64_t>(s.Sq),
+                              static_cast<uint64_t>(s.H), static_cast<uint64_t>(s.B)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(a.er_stride_q) * 4, static_cast<uint64_t>(a.er_stride_h) * 4,
+                                 static_cast<uint64_t>(a.er_stride_b) * 4};
+    const uint32_t box[4] = {32, 128, 1, 1};
+    if (tma_host::make_f32_map_sw128(&mn, a.exp_rand, dims, strides, box) != 0) return cudaErrorInvalidValue;
+    auto kern = s.bf16 ? kf_rowstat_kernel<true, true> : kf_rowstat_kernel<false, true>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<true>::kSmem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kRsThreads, RsCfg<true>::kSmem, stream>>>(mq, mk, mn, p, lse2_out);
+  } else {
+    auto kern = s.bf16 ? kf_rowstat_kernel<true, false> : kf_rowstat_kernel<false, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<false>::kSmem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kRsThreads, RsCfg<false>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
+  }
   count_launch();
   return cudaPeekAtLastError();
 }

@@ -48,4 +48,21 @@ inline int make_bshd_map(CUtensorMap* map, const void* base, bool is_bf16, int64
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// A 4-D f32 tensor (innermost stride 1; `strides` in BYTES for dimensions 1..3, multiples of 16)
+// tiled with the 128-byte swizzle: box[0] must be 32 elements (128 bytes).  Out-of-range elements
+// read as zero.  Returns 0 on success.
+inline int make_f32_map_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                              const uint64_t strides[3], const uint32_t box[4]) {
+  encode_tiled_fn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t st[3] = {strides[0], strides[1], strides[2]};
+  cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), d, st, bx, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 }  // namespace tma_host

@@ -110,7 +110,7 @@ def test_roco_vs_oracle(ops, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(1, 256, 256, 2), (2, 640, 640, 2), (1, 130, 300, 1)])
+@pytest.mark.parametrize("shape", [(1, 256, 256, 2), (2, 640, 640, 2), (1, 130, 300, 1), (1, 100, 333, 2)])
 def test_keyformer_vs_oracle(ops, shape, dtype):
   B, Sq, Skv, H = shape
   q, k, v, er = O.make_inputs("keyformer", B, Sq, Skv, H, 128, dtype, seed=9)
