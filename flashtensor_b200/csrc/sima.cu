@@ -11,8 +11,9 @@
 //                          column sums of |K| and |Q| with 128-bit shared-memory loads.  Partial
 //                          results go to the workspace.
 //   2. sima_reduce_kernel  sums the partials in a fixed order, divides by ck*cq, and writes M'^T in
-//                          the 16-bit input type scaled by a per-head power of two (the entries are
-//                          ~1e-6, far below fp16's normal range), plus the inverse scale.
+//                          the 16-bit input type scaled by a power of two per block of 32 output
+//                          channels (the entries are ~1e-6, far below fp16's normal range), plus
+//                          the inverse scales.
 //   3. sima_out_kernel     streams Q again: out = (Q M'') * inverse scale, tcgen05 with the
 //                          accumulator double-buffered in TMEM, TMA store.
 #include <cuda_bf16.h>
@@ -41,7 +42,7 @@ struct SimaWs {
   float* part_m;     // [BH][nchunks][e][d]  partial (K^T V)^T
   float* part_c;     // [BH][nchunks][2][128] partial ck, cq
   uint16_t* m16;     // [BH][e][d] scaled M'^T in the input type
-  float* inv_scale;  // [BH]
+  float* inv_scale;  // [BH][4]: one per block of 32 output channels
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -239,14 +240,19 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // 2. reduce partials, normalise, scale into the 16-bit type.  part_m and the output m16 are
 //    both stored [e][d] (d contiguous): the K-major B operand of step 3.
 // ---------------------------------------------------------------------------------------------
+// One CTA per (head, block of 32 output channels e): 4096 entries of M'^T, its own power-of-two
+// scale (the epilogue of step 3 multiplies each 32-column chunk by the matching inverse).
+constexpr int kRedBlocks = 4;
+constexpr int kRedElems = kMElems / kRedBlocks;
 template <bool kBF16>
-__global__ void __launch_bounds__(256, 1) sima_reduce_kernel(const StatsParams p) {
+__global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p) {
   __shared__ float inv_c[kTile];
   __shared__ float wmax[8];
   __shared__ float s_scale;
-  const int bh = blockIdx.x, tid = threadIdx.x;
+  const int blk = blockIdx.x % kRedBlocks;
+  const int bh = blockIdx.x / kRedBlocks, tid = threadIdx.x;
   const float* pc = p.ws.part_c + static_cast<size_t>(bh) * p.nchunks * 2 * kTile;
-  const float* pm = p.ws.part_m + static_cast<size_t>(bh) * p.nchunks * kMElems;
+  const float* pm = p.ws.part_m + static_cast<size_t>(bh) * p.nchunks * kMElems + blk * kRedElems;
   if (tid < kTile) {
     float ck = 0.f, cq = 0.f;
     for (int c = 0; c < p.nchunks; ++c) {
@@ -256,11 +262,11 @@ __global__ void __launch_bounds__(256, 1) sima_reduce_kernel(const StatsParams p
     inv_c[tid] = __fdiv_rn(1.0f, __fmul_rn(ck, cq));
   }
   __syncthreads();
-  float vals[kMElems / 256];
+  float vals[kRedElems / 256];
   float amax = 0.f;
 #pragma unroll
-  for (int it = 0; it < kMElems / 256; ++it) {
-    const int idx = it * 256 + tid;  // = e * 128 + d
+  for (int it = 0; it < kRedElems / 256; ++it) {
+    const int idx = it * 256 + tid;  // = e_local * 128 + d
     float m = 0.f;
     for (int c = 0; c < p.nchunks; ++c) m += pm[static_cast<size_t>(c) * kMElems + idx];
     m *= inv_c[idx & 127];
@@ -281,13 +287,13 @@ __global__ void __launch_bounds__(256, 1) sima_reduce_kernel(const StatsParams p
       sc = ldexpf(1.0f, 14 - ex);  // a * sc in [2^13, 2^14)
     }
     s_scale = sc;
-    p.ws.inv_scale[bh] = 1.0f / sc;
+    p.ws.inv_scale[bh * kRedBlocks + blk] = 1.0f / sc;
   }
   __syncthreads();
   const float sc = s_scale;
-  uint16_t* dst = p.ws.m16 + static_cast<size_t>(bh) * kMElems;
+  uint16_t* dst = p.ws.m16 + static_cast<size_t>(bh) * kMElems + blk * kRedElems;
 #pragma unroll
-  for (int it = 0; it < kMElems / 256; ++it) {
+  for (int it = 0; it < kRedElems / 256; ++it) {
     const int idx = it * 256 + tid;
     const float v = vals[it] * sc;
     uint16_t bits;
@@ -425,7 +431,9 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int wq = warp & 3;
     const int r = wq * 32 + lane;  // row of the tile
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const float inv_sc = p.inv_scale[bh];
+    // one inverse scale per block of 32 output channels = per TMEM chunk below
+    const float inv4[4] = {p.inv_scale[bh * 4 + 0], p.inv_scale[bh * 4 + 1], p.inv_scale[bh * 4 + 2],
+                           p.inv_scale[bh * 4 + 3]};
     bool ok = true;
     for (int i = 0; i < ntile; ++i) {
       const int buf = i & 1;
@@ -444,6 +452,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         uint32_t u[32];
         tmem_ld32(tbase + lane_base + buf * 128 + c * 32, u);
         tmem_wait_ld();
+        const float inv_sc = inv4[c];
         if constexpr (kOutF32) {
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
@@ -536,7 +545,7 @@ Plan make_plan(const SimaShape& s) {
   pl.off_pm = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * kMElems * 4);
   pl.off_pc = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * 2 * kTile * 4);
   pl.off_m16 = off; off = align256(off + static_cast<size_t>(bh) * kMElems * 2);
-  pl.off_sc = off; off = align256(off + static_cast<size_t>(bh) * 4);
+  pl.off_sc = off; off = align256(off + static_cast<size_t>(bh) * kRedBlocks * 4);
   pl.total = off;
   return pl;
 }
@@ -572,7 +581,7 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   }
   {
     auto kern = s.bf16 ? sima_reduce_kernel<true> : sima_reduce_kernel<false>;
-    kern<<<bh, 256, 0, stream>>>(sp);
+    kern<<<bh * kRedBlocks, 256, 0, stream>>>(sp);
     count_launch();
     if ((e = cudaPeekAtLastError()) != cudaSuccess) return e;
   }
