@@ -42,6 +42,8 @@ WORKLOADS = {
                 desc="H2O prefill fp16 B1 H32 S4096 D128, top-k S/8 + 256 recent"),
     "keyformer": dict(B=4, H=32, S=2048, dtype="f16", k_keep=512, tau=1.5,
                       desc="Keyformer prefill fp16 B4 H32 S2048 D128 tau 1.5, top-k S/4, exp_rand operand"),
+    "keyformer_seeded": dict(B=4, H=32, S=2048, dtype="f16", k_keep=512, tau=1.5, seed=2024,
+                             desc="Keyformer prefill fp16 B4 H32 S2048 D128 tau 1.5, top-k S/4, Gumbel noise from seed"),
     "roco": dict(B=2, H=40, S=4096, dtype="bf16", k_keep=512,
                  desc="RoCo prefill bf16 B2 H40 S4096 D128, top-k S/8 by mean then std"),
     "sima": dict(B=8, H=32, S=8192, dtype="f16", desc="SimA fp16 B8 H32 S8192 D128 non-causal"),
@@ -75,7 +77,7 @@ def io_bytes_of(case, w, batch):
   """Compulsory traffic: every input and output once at its storage width."""
   n = batch * w["S"] * w["H"] * 128 * 2
   total = 4 * n
-  if case in ("h2o", "keyformer"):
+  if case in ("h2o", "keyformer", "keyformer_seeded"):
     total += batch * w["H"] * w["S"] * 4
   if case == "roco":
     total += 2 * batch * w["H"] * w["S"] * 4
@@ -170,6 +172,9 @@ def build_step(case, w):
   if case == "keyformer":
     m = ft.KeyFormer(tau=w["tau"], head_num=H, kv_head_num=H)
     return lambda q, k, v, er: m.select(q, k, v, er, w["k_keep"])
+  if case == "keyformer_seeded":
+    m = ft.KeyFormer(tau=w["tau"], head_num=H, kv_head_num=H)
+    return lambda q, k, v: m.seeded(q, k, v, w["seed"], w["k_keep"])
   m = ft.SimA(head_num=H, kv_head_num=H)
   return lambda q, k, v: (m(q, k, v),)
 
@@ -204,7 +209,9 @@ def cpu_oracle_sample(case, w, heads, threads):
   elif case == "roco":
     _, s, s2 = O.roco(*ins)
     O.roco_select(s.numpy(), s2.numpy(), w["k_keep"], w["S"])
-  elif case == "keyformer":
+  elif case in ("keyformer", "keyformer_seeded"):
+    if case == "keyformer_seeded":
+      ins = ins[:3] + [O.keyformer_seeded_exp_rand(w["seed"], 1, heads, w["S"], w["S"])]
     _, s = O.keyformer(*ins, tau=w["tau"])
     O.keyformer_select(s.numpy(), w["k_keep"])
   else:

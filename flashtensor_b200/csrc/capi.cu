@@ -178,12 +178,16 @@ int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a)
     if (!(p->tau > 0.f) || std::isinf(p->tau)) return ASUKA_ERR_BAD_ARGUMENT;
     a->tau = p->tau;
     a->seed = p->seed;
-    if (p->exp_rand.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;  // seeded generator: not built yet
-    if ((r = check_er(p->exp_rand, c->s)) != ASUKA_OK) return r;
-    a->exp_rand = static_cast<const float*>(p->exp_rand.ptr);
-    a->er_stride_b = p->exp_rand.stride[0];
-    a->er_stride_h = p->exp_rand.stride[1];
-    a->er_stride_q = p->exp_rand.stride[2];
+    if (p->exp_rand.ptr != nullptr) {
+      if ((r = check_er(p->exp_rand, c->s)) != ASUKA_OK) return r;
+      a->exp_rand = static_cast<const float*>(p->exp_rand.ptr);
+      a->er_stride_b = p->exp_rand.stride[0];
+      a->er_stride_h = p->exp_rand.stride[1];
+      a->er_stride_q = p->exp_rand.stride[2];
+    } else {
+      // seeded noise: the generator packs (q, kv) into one 32-bit word
+      if (c->s.Sq > 65536 || c->s.Skv > 65536) return ASUKA_ERR_TOO_LARGE;
+    }
   } else if (rowstat) {
     return ASUKA_ERR_BAD_ARGUMENT;
   }

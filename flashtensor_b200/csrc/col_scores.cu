@@ -50,6 +50,7 @@ struct ColParams {
   float* score_sq;
   const float* exp_rand;
   int64_t er_sb, er_sh, er_sq;
+  uint64_t seed;
   uint32_t* status;
 };
 
@@ -69,12 +70,38 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Seeded Keyformer noise: one bijective 32-bit mix ("lowbias32") per logit.
+//   head_key = hash(seed_lo ^ hash((b*H + h) ^ seed_hi));  word = hash(((q << 16) ^ kv) ^ head_key)
+//   u = ((word >> 9) + 0.5) * 2^-23 in (0,1);  exp_rand = -ln(u);  noise g = -ln(exp_rand) ~ Gumbel(0,1)
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ uint32_t seeded_head_key(uint64_t seed, uint32_t bh) {
+  return hash_u32(static_cast<uint32_t>(seed) ^ hash_u32(bh ^ static_cast<uint32_t>(seed >> 32)));
+}
+// log2(exp_rand) of logit (q, kv): exp_rand = -ln(u) = -lg2(u) * ln 2
+__device__ __forceinline__ float seeded_lg2_exp_rand(uint32_t q, uint32_t kv, uint32_t head_key) {
+  const uint32_t w = hash_u32(((q << 16) ^ kv) ^ head_key);
+  const float u = __uint_as_float(0x3f800000u | (w >> 9)) + (-1.0f + 5.9604645e-8f);  // exact
+  // -ln(u): the hardware log2 has a fixed ABSOLUTE error, useless for u next to 1 (where the
+  // large, row-dominating Gumbel values come from); there use the series in d = 1 - u (exact)
+  const float d = 1.0f - u;
+  const float series = d * fmaf(d, fmaf(d, 0.33333334f, 0.5f), 1.0f);
+  const float er = d < 0.015625f ? series : -0.69314718f * lg2(u);
+  return lg2(er);
+}
+
 __device__ __forceinline__ void record_timeout(uint32_t* status, uint32_t site) {
   atomicAdd(&status[0], 1u);
   status[1] = site;
 }
 
-// kMode: 0 sum, 1 sum + sum of squares, 2 perturbed (noise operand)
+// kMode: 0 sum, 1 sum + sum of squares, 2 perturbed (noise operand), 3 perturbed (seeded noise)
 template <bool kBF16, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -236,6 +263,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     float acc2[4] = {0.f, 0.f, 0.f, 0.f};
     bool ok = true;
+    const uint32_t head_key = kMode == 3 ? seeded_head_key(p.seed, static_cast<uint32_t>(bh)) : 0u;
     const float* er_col = nullptr;
     if constexpr (kMode == 2) {
       er_col = p.exp_rand + static_cast<int64_t>(b) * p.er_sb + static_cast<int64_t>(h) * p.er_sh +
@@ -294,6 +322,10 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 float x;
                 if constexpr (kMode == 2) {
                   x = fmaf(s[cc], scale, fmaf(lg2(noise[cc]), -p.inv_tau, -lv[e]));
+                } else if constexpr (kMode == 3) {
+                  const float l2 = seeded_lg2_exp_rand(static_cast<uint32_t>(i * kTile + hc * 64 + cc),
+                                                       static_cast<uint32_t>(key), head_key);
+                  x = fmaf(s[cc], scale, fmaf(l2, -p.inv_tau, -lv[e]));
                 } else {
                   x = fmaf(s[cc], scale, -lv[e]);
                 }
@@ -340,8 +372,9 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // ---------------------------------------------------------------------------------------------
 constexpr int kRsThreads = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 rows
 constexpr uint32_t kNoiseTileBytes = 128 * 128 * 4;
-template <bool kNoiseTma> struct RsCfg {
-  static constexpr int kStages = kNoiseTma ? 2 : 4;
+template <int kNoise> struct RsCfg {  // kNoise 1: the noise tile shares the stage with K
+  static constexpr bool kNoiseTma = kNoise == 1;
+  static constexpr int kStages = kNoise == 0 ? 4 : 2;  // seeded: small enough for two CTAs per SM
   static constexpr uint32_t kStageBytes = kTileBytes + (kNoiseTma ? kNoiseTileBytes : 0);
   static constexpr uint32_t kSmem = kTileBytes + kStages * kStageBytes + 1024;
 };
@@ -352,11 +385,13 @@ struct RsBars {
   uint64_t s_full[2], s_empty[2];
 };
 
-template <bool kBF16, bool kNoiseTma>
-__global__ void __launch_bounds__(kRsThreads, 1)
+// kNoise: 0 noise operand read directly, 1 noise operand staged by TMA, 2 seeded noise
+template <bool kBF16, int kNoise>
+__global__ void __launch_bounds__(kRsThreads, kNoise == 2 ? 2 : 1)
 kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_n, const ColParams p, float* lse_out) {
-  using Cfg = RsCfg<kNoiseTma>;
+  constexpr bool kNoiseTma = kNoise == 1;
+  using Cfg = RsCfg<kNoise>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) RsBars bars;
@@ -471,9 +506,11 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     int lim = p.Skv - 1;
     if (p.causal) lim = min(lim, row + p.diag_off);
     const float scale = p.scale_log2;
-    const float* er_row = p.exp_rand + static_cast<int64_t>(b) * p.er_sb +
-                          static_cast<int64_t>(h) * p.er_sh +
-                          static_cast<int64_t>(min(row, p.Sq - 1)) * p.er_sq;
+    const float* er_row = kNoise == 2 ? nullptr
+                                      : p.exp_rand + static_cast<int64_t>(b) * p.er_sb +
+                                            static_cast<int64_t>(h) * p.er_sh +
+                                            static_cast<int64_t>(min(row, p.Sq - 1)) * p.er_sq;
+    const uint32_t head_key = kNoise == 2 ? seeded_head_key(p.seed, static_cast<uint32_t>(bh)) : 0u;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
@@ -497,7 +534,7 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const float4 v = *reinterpret_cast<const float4*>(box + sw128_offset(r_in_tile, ch));
             er[ch * 4 + 0] = v.x; er[ch * 4 + 1] = v.y; er[ch * 4 + 2] = v.z; er[ch * 4 + 3] = v.w;
           }
-        } else {
+        } else if constexpr (kNoise == 0) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) er[e] = __ldg(er_row + min(j * kTile + c4 * 32 + e, p.Skv - 1));
         }
@@ -507,7 +544,13 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int cc = c4 * 32 + e;
-          const float v = fmaf(__uint_as_float(u[e]), scale, -lg2(er[e]) * p.inv_tau);
+          float l2;
+          if constexpr (kNoise == 2) {
+            l2 = seeded_lg2_exp_rand(static_cast<uint32_t>(row), static_cast<uint32_t>(j * kTile + cc), head_key);
+          } else {
+            l2 = lg2(er[e]);
+          }
+          const float v = fmaf(__uint_as_float(u[e]), scale, -l2 * p.inv_tau);
           x[e] = (cc > thr) ? -INFINITY : v;
           mt4[e & 3] = fmaxf(mt4[e & 3], x[e]);
         }
@@ -561,6 +604,7 @@ ColParams make_params(const ScoreArgs& a, const AttnShape& s) {
   p.er_sb = a.er_stride_b;
   p.er_sh = a.er_stride_h;
   p.er_sq = a.er_stride_q;
+  p.seed = a.seed;
   p.status = device_status_words();
   return p;
 }
@@ -575,7 +619,8 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
   void (*kern)(CUtensorMap, CUtensorMap, ColParams) = nullptr;
   if (a.mode == ASUKA_SCORE_SUM) kern = s.bf16 ? col_scores_kernel<true, 0> : col_scores_kernel<false, 0>;
   else if (a.mode == ASUKA_SCORE_SUM_SQ) kern = s.bf16 ? col_scores_kernel<true, 1> : col_scores_kernel<false, 1>;
-  else kern = s.bf16 ? col_scores_kernel<true, 2> : col_scores_kernel<false, 2>;
+  else if (a.exp_rand != nullptr) kern = s.bf16 ? col_scores_kernel<true, 2> : col_scores_kernel<false, 2>;
+  else kern = s.bf16 ? col_scores_kernel<true, 3> : col_scores_kernel<false, 3>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
   kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, p);
@@ -587,11 +632,19 @@ cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, cons
                               float* lse2_out, const AttnShape& s, cudaStream_t stream) {
   const ColParams p = make_params(a, s);
   const dim3 grid(static_cast<unsigned>(p.nq_tiles) * s.B * s.H);
+  cudaError_t e;
+  if (a.exp_rand == nullptr) {
+    auto kern = s.bf16 ? kf_rowstat_kernel<true, 2> : kf_rowstat_kernel<false, 2>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<2>::kSmem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kRsThreads, RsCfg<2>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
+    count_launch();
+    return cudaPeekAtLastError();
+  }
   // TMA needs a 16-byte aligned base and strides that are multiples of 16 bytes
   const bool tma_ok = (reinterpret_cast<uintptr_t>(a.exp_rand) & 15u) == 0 && a.er_stride_q % 4 == 0 &&
                       a.er_stride_h % 4 == 0 && a.er_stride_b % 4 == 0 && a.er_stride_q > 0 &&
                       a.er_stride_h > 0 && a.er_stride_b > 0;
-  cudaError_t e;
   if (tma_ok) {
     CUtensorMap mn;
     const uint64_t dims[4] = {static_cast<uint64_t>(s.Skv), static_cast<uint64_t>(s.Sq),
@@ -600,15 +653,15 @@ cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, cons
                                  static_cast<uint64_t>(a.er_stride_b) * 4};
     const uint32_t box[4] = {32, 128, 1, 1};
     if (tma_host::make_f32_map_sw128(&mn, a.exp_rand, dims, strides, box) != 0) return cudaErrorInvalidValue;
-    auto kern = s.bf16 ? kf_rowstat_kernel<true, true> : kf_rowstat_kernel<false, true>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<true>::kSmem);
+    auto kern = s.bf16 ? kf_rowstat_kernel<true, 1> : kf_rowstat_kernel<false, 1>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<1>::kSmem);
     if (e != cudaSuccess) return e;
-    kern<<<grid, kRsThreads, RsCfg<true>::kSmem, stream>>>(mq, mk, mn, p, lse2_out);
+    kern<<<grid, kRsThreads, RsCfg<1>::kSmem, stream>>>(mq, mk, mn, p, lse2_out);
   } else {
-    auto kern = s.bf16 ? kf_rowstat_kernel<true, false> : kf_rowstat_kernel<false, false>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<false>::kSmem);
+    auto kern = s.bf16 ? kf_rowstat_kernel<true, 0> : kf_rowstat_kernel<false, 0>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<0>::kSmem);
     if (e != cudaSuccess) return e;
-    kern<<<grid, kRsThreads, RsCfg<false>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
+    kern<<<grid, kRsThreads, RsCfg<0>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
   }
   count_launch();
   return cudaPeekAtLastError();

@@ -88,8 +88,9 @@ def test_select_and_case_validation_codes(built_lib):
   assert need.value >= 2 * 256 * 4
   assert lib.asuka_b200_h2o(ctypes.byref(cp), ctypes.c_void_p(0x1000), 16, None) == -6
   assert lib.asuka_b200_h2o(ctypes.byref(cp), None, need.value, None) == -1
-  # Keyformer without a noise operand
-  assert lib.asuka_b200_keyformer(ctypes.byref(cp), ctypes.c_void_p(0x1000), need.value, None) == -1
+  # Keyformer: a bad temperature is refused (tau is 1.0 above, make it 0)
+  cp.tau = 0.0
+  assert lib.asuka_b200_keyformer(ctypes.byref(cp), ctypes.c_void_p(0x1000), need.value, None) == -10
   sp = _lib.SimaParams(_t(shp), _t(shp), _t((1, 128, 2, 128)), _t(shp))
   assert lib.asuka_b200_sima_workspace_bytes(ctypes.byref(sp), ctypes.byref(need)) == -3
 

@@ -97,15 +97,18 @@ def test_tie_rule_comparator():
     O.check_index_sets(far, want, keys, 2)
 
 
-def test_philox_is_a_bijection_on_small_counters_and_stable():
-  c = np.arange(4096, dtype=np.uint32)
-  z = np.zeros_like(c)
-  w = O.philox4x32_10(c, z, z, z, 7, 9)
-  again = O.philox4x32_10(c, z, z, z, 7, 9)
-  assert all(np.array_equal(a, b) for a, b in zip(w, again))
-  packed = (w[0].astype(np.uint64) << np.uint64(32)) | w[1].astype(np.uint64)
-  assert len(np.unique(packed)) == 4096
-  u = ((w[0] >> np.uint32(8)).astype(np.float64) + 0.5) * 2.0 ** -24
-  assert 0.45 < u.mean() < 0.55 and u.min() > 0 and u.max() < 1
-  er = O.keyformer_seeded_exp_rand(3, 1, 2, 8, 16)
-  assert er.shape == (1, 2, 8, 16) and torch.all(er > 0)
+def test_seeded_noise_generator():
+  x = np.arange(1 << 16, dtype=np.uint32)
+  h = O.hash_u32(x)
+  assert len(np.unique(h)) == len(x)                      # a bijection never collides
+  assert int(O.hash_u32(np.uint32(0))) == 0               # 0 is the mixer's fixed point
+  w = O.keyformer_seeded_bits(3, 1, 2, 64, 128)
+  assert w.shape == (1, 2, 64, 128)
+  assert len(np.unique(w[0, 0])) == 64 * 128               # distinct word per logit of a head
+  assert not np.array_equal(w[0, 0], w[0, 1])              # heads differ
+  assert not np.array_equal(w, O.keyformer_seeded_bits(4, 1, 2, 64, 128))
+  assert np.array_equal(w, O.keyformer_seeded_bits(3, 1, 2, 64, 128))
+  er = O.keyformer_seeded_exp_rand(3, 2, 2, 256, 256)
+  assert er.shape == (2, 2, 256, 256) and torch.all(er > 0) and torch.isfinite(er).all()
+  g = -er.double().log()                                   # Gumbel(0,1): mean 0.5772, var pi^2/6
+  assert abs(g.mean().item() - 0.5772) < 0.02 and abs(g.var().item() - 1.6449) < 0.05

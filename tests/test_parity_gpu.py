@@ -124,6 +124,33 @@ def test_keyformer_vs_oracle(ops, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 256, 256, 2), (2, 640, 640, 3), (1, 100, 333, 2)])
+def test_keyformer_seeded_noise_vs_oracle(ops, shape, dtype):
+  # Gumbel noise generated in the kernels from a seed; the oracle restates the generator, turns it
+  # into the exp_rand operand of the unmodified Keyformer definition, and must agree
+  import flashtensor_b200 as ft
+  B, Sq, Skv, H = shape
+  q, k, v = O.make_inputs("attn", B, Sq, Skv, H, 128, dtype, seed=19)
+  seed = 0x1234567_89ABCDEF
+  er = O.keyformer_seeded_exp_rand(seed, B, H, Sq, Skv)
+  ref_out, ref_score = O.keyformer(q, k, v, er, tau=1.5)
+  model = ft.KeyFormer(tau=1.5, head_num=H, kv_head_num=H)
+  out, score, idx = model.seeded(q.cuda(), k.cuda(), v.cuda(), seed, k_keep=Skv // 4)
+  torch.cuda.synchronize()
+  close(out, ref_out, "out")
+  close(score, ref_score, "kf_score (seeded)")
+  # the operand path fed with the same noise gives the same scores
+  _, score_op = ops.keyformer(q.cuda(), k.cuda(), v.cuda(), er.cuda(), tau=1.5)
+  torch.testing.assert_close(score, score_op, rtol=1e-4, atol=1e-5)
+  # a different seed gives different scores; the same seed reproduces bit for bit
+  _, score2 = model.seeded(q.cuda(), k.cuda(), v.cuda(), seed + 1)
+  _, score3 = model.seeded(q.cuda(), k.cuda(), v.cuda(), seed)
+  assert not torch.equal(score, score2) and torch.equal(score, score3)
+  assert np.array_equal(idx.cpu().numpy(), O.keyformer_select(score.cpu().numpy(), Skv // 4))
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 128, 1), (2, 1000, 3), (1, 4096, 2), (1, 77, 2)])
 def test_sima_vs_oracle(ops, shape, dtype):
   B, S, H = shape
