@@ -6,16 +6,20 @@
 // for the second product, f32 accumulation, fully masked tiles skipped (the numerics fixed by
 // LowerComplexReduce / RecoverTypeInKernel / ReplaceExpAndLog / EquivalentTransform / DynamicFor).
 //
-// One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong through the
-// tensor pipe so that the softmax of one overlaps the MMAs of the other.
+// The kernel is persistent: one CTA per SM walks a list of work items (256 query rows of one
+// (batch, head), heaviest first, dealt out in a zigzag so that every CTA gets the same amount of
+// work).  The two 128-row tiles of an item ping-pong through the tensor pipe so that the softmax of
+// one overlaps the MMAs of the other, and the K/V/Q loads and the first QK^T of the next item run
+// under the tail and the epilogue of the current one.
 //   warp 0        TMA producer: Q once, then K tiles of 128 keys through a 3-stage ring
 //   warp 2        TMA producer: V tiles through a 2-stage ring
 //   warp 1        issues tcgen05.mma: S_t = Q_t K^T (SMEM x SMEM), O_t += P_t V (TMEM x SMEM)
 //   warps 4-7     softmax of tile 0: one thread per query row, whole row of S in registers
 //   warps 8-11    softmax of tile 1
 // TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 f32 columns each; P_t (16-bit, 64 columns)
-// overwrites the front of S_t once S_t is in registers.  The running maximum is only refreshed
-// when it grows by more than 2^8, so O is rescaled (a TMEM round trip) almost never.
+// overwrites the front of S_t once S_t is in registers.  The exponent reference of a row is only
+// moved when a tile's row sum would overflow the stale one, so O is rescaled (a TMEM round trip)
+// almost never.  The epilogue writes O_t / l from registers straight to global memory.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -42,17 +46,19 @@ constexpr float kRescaleLimit = 8192.0f;  // largest tile row sum tolerated unde
 struct FwdParams {
   int B, H, Sq, Skv;
   int causal, diag_off;
-  int nq_blocks;
+  int nq_blocks, n_items;
   float scale_log2;
   float* lse2;
+  void* out;                 // [B, Sq, H, 128], 16-bit, strides in elements
+  int64_t o_sb, o_ss, o_sh;
   uint32_t* status;
 };
 
 struct Bars {
-  uint64_t q_full[2];
+  uint64_t q_full[2], q_empty[2];
   uint64_t k_full[kKStages], k_empty[kKStages];
   uint64_t v_full[kVStages], v_empty[kVStages];
-  uint64_t s_full[2], p_ready[2], o_done[2], epi[2];
+  uint64_t s_full[2], p_ready[2], o_done[2], o_free[2];
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -97,18 +103,48 @@ __device__ __forceinline__ int kv_tiles_for(int q0, const FwdParams& p) {
   return last / kTile + 1;
 }
 
+// One work item: 256 query rows of one (batch, head).
+struct Item {
+  int b, h;
+  int q0[2];    // first row of each 128-row tile
+  int n_kv[2];  // 128-key tiles each tile visits (0: the tile lies past the end of the sequence)
+  int n_max;
+};
+
+// The it-th item of this CTA.  Items are sorted heaviest first; wave w of gridDim.x items is dealt
+// out forwards when w is even and backwards when it is odd, which evens out the totals.
+__device__ __forceinline__ bool get_item(int it, const FwdParams& p, Item* item) {
+  const int G = static_cast<int>(gridDim.x);
+  const int r = static_cast<int>(blockIdx.x);
+  const int idx = it * G + ((it & 1) ? G - 1 - r : r);
+  if (idx >= p.n_items) return false;
+  const int bh_count = p.B * p.H;
+  const int qb = p.nq_blocks - 1 - idx / bh_count;
+  const int bh = idx % bh_count;
+  item->b = bh / p.H;
+  item->h = bh % p.H;
+  item->q0[0] = qb * 2 * kTile;
+  item->q0[1] = qb * 2 * kTile + kTile;
+  item->n_kv[0] = kv_tiles_for(item->q0[0], p);
+  item->n_kv[1] = kv_tiles_for(item->q0[1], p);
+  item->n_max = max(item->n_kv[0], item->n_kv[1]);
+  return true;
+}
+// with an odd number of waves the last, backwards-dealt wave can skip a CTA that still has none
+__device__ __forceinline__ int item_waves(const FwdParams& p) {
+  return (p.n_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+}
+
 template <bool kBF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                const FwdParams p) {
+                const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) Bars bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base;                          // 2 tiles
   const uint32_t sK = smem_base + 2 * kTileBytes;         // kKStages tiles
   const uint32_t sV = sK + kKStages * kTileBytes;         // kVStages tiles
@@ -117,24 +153,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int warp = tid >> 5;
   const int lane = tid & 31;
   volatile uint32_t* abortp = &abort_s;
-
-  // work item: heaviest (latest) query blocks first
-  const int bh_count = p.B * p.H;
-  const int qb = p.nq_blocks - 1 - static_cast<int>(blockIdx.x) / bh_count;
-  const int bh = static_cast<int>(blockIdx.x) % bh_count;
-  const int b = bh / p.H, h = bh % p.H;
-  const int q0[2] = {qb * 2 * kTile, qb * 2 * kTile + kTile};
-  const int n_kv[2] = {kv_tiles_for(q0[0], p), kv_tiles_for(q0[1], p)};
-  const int n_max = max(n_kv[0], n_kv[1]);
+  const int n_waves = item_waves(p);
 
   if (tid == 0) {
     abort_s = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars.q_full[i]), 1);
+      mbar_init(smem_u32(&bars.q_empty[i]), 1);
       mbar_init(smem_u32(&bars.s_full[i]), 1);
       mbar_init(smem_u32(&bars.p_ready[i]), 128);
       mbar_init(smem_u32(&bars.o_done[i]), 1);
-      mbar_init(smem_u32(&bars.epi[i]), 128);
+      mbar_init(smem_u32(&bars.o_free[i]), 128);
     }
     for (int i = 0; i < kKStages; ++i) {
       mbar_init(smem_u32(&bars.k_full[i]), 1);
@@ -148,7 +177,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
-    tma_prefetch_desc(&map_o);
   }
   if (warp == 1) {
     __syncwarp();
@@ -160,64 +188,78 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
 
+  // Every role walks the same item list and keeps running counts (K tiles, V tiles, tile steps,
+  // items per tile) from which ring stages and barrier parities follow; nothing is reset
+  // between items.
   // 384 threads x 168 registers: the four utility warps hand most of theirs to the softmax warps
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer: Q and K
     reg_dealloc<kUtilRegs>();
     if (lane == 0) {
       bool ok = true;
-      for (int t = 0; t < 2; ++t) {
-        if (n_kv[t] > 0) {
+      uint32_t kc = 0;            // K tiles issued so far
+      uint32_t qn[2] = {0, 0};    // items in which tile t was loaded so far
+      Item it_;
+      for (int it = 0; it < n_waves && ok; ++it) {
+        if (!get_item(it, p, &it_)) continue;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (it_.n_kv[t] == 0) continue;
+          if (qn[t] > 0) {  // the previous item's last QK^T of this tile must have read Q_t
+            ok = mbar_wait(smem_u32(&bars.q_empty[t]), (qn[t] - 1) & 1, abortp);
+            if (!ok) { record_timeout(p.status, 11); break; }
+          }
           const uint32_t bar = smem_u32(&bars.q_full[t]);
           mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(sQ + t * kTileBytes, &map_q, bar, 0, h, q0[t], b);
-          tma_load_4d(sQ + t * kTileBytes + kHalfBytes, &map_q, bar, 64, h, q0[t], b);
+          tma_load_4d(sQ + t * kTileBytes, &map_q, bar, 0, it_.h, it_.q0[t], it_.b);
+          tma_load_4d(sQ + t * kTileBytes + kHalfBytes, &map_q, bar, 64, it_.h, it_.q0[t], it_.b);
+          ++qn[t];
         }
-      }
-      int issued = 0;
-      for (int j = 0; j < n_max; ++j) {
-        const int st = j % kKStages;
-        const uint32_t use = static_cast<uint32_t>(j / kKStages);
-        if (use > 0) {
-          ok = mbar_wait(smem_u32(&bars.k_empty[st]), (use - 1) & 1, abortp);
-          if (!ok) { record_timeout(p.status, 1); break; }
+        for (int j = 0; j < it_.n_max && ok; ++j, ++kc) {
+          const int st = kc % kKStages;
+          const uint32_t use = kc / kKStages;
+          if (use > 0) {
+            ok = mbar_wait(smem_u32(&bars.k_empty[st]), (use - 1) & 1, abortp);
+            if (!ok) { record_timeout(p.status, 1); break; }
+          }
+          const uint32_t bar = smem_u32(&bars.k_full[st]);
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, it_.h, j * kTile, it_.b);
+          tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, it_.h, j * kTile, it_.b);
         }
-        const uint32_t bar = smem_u32(&bars.k_full[st]);
-        mbar_expect_tx(bar, kTileBytes);
-        tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, h, j * kTile, b);
-        tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
-        issued = j + 1;
       }
       if (!ok) {
         // give copies already in flight a bounded chance to land before the CTA retires
         volatile uint32_t none = 0;
-        for (int j = max(0, issued - kKStages); j < issued; ++j)
-          mbar_wait(smem_u32(&bars.k_full[j % kKStages]), (j / kKStages) & 1, &none);
+        for (uint32_t c = kc > kKStages ? kc - kKStages : 0; c < kc; ++c)
+          mbar_wait(smem_u32(&bars.k_full[c % kKStages]), (c / kKStages) & 1, &none);
       }
     }
   } else if (warp == 2) {
-    // ------------------------------------------------------------------ TMA producer for V
+    // ------------------------------------------------------------------ TMA producer: V
     reg_dealloc<kUtilRegs>();
     if (lane == 0) {
       bool ok = true;
-      int issued = 0;
-      for (int j = 0; j < n_max; ++j) {
-        const int st = j % kVStages;
-        const uint32_t use = static_cast<uint32_t>(j / kVStages);
-        if (use > 0) {
-          ok = mbar_wait(smem_u32(&bars.v_empty[st]), (use - 1) & 1, abortp);
-          if (!ok) { record_timeout(p.status, 2); break; }
+      uint32_t vc = 0;
+      Item it_;
+      for (int it = 0; it < n_waves && ok; ++it) {
+        if (!get_item(it, p, &it_)) continue;
+        for (int j = 0; j < it_.n_max && ok; ++j, ++vc) {
+          const int st = vc % kVStages;
+          const uint32_t use = vc / kVStages;
+          if (use > 0) {
+            ok = mbar_wait(smem_u32(&bars.v_empty[st]), (use - 1) & 1, abortp);
+            if (!ok) { record_timeout(p.status, 2); break; }
+          }
+          const uint32_t bar = smem_u32(&bars.v_full[st]);
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, it_.h, j * kTile, it_.b);
+          tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, it_.h, j * kTile, it_.b);
         }
-        const uint32_t bar = smem_u32(&bars.v_full[st]);
-        mbar_expect_tx(bar, kTileBytes);
-        tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, h, j * kTile, b);
-        tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, h, j * kTile, b);
-        issued = j + 1;
       }
       if (!ok) {
         volatile uint32_t none = 0;
-        for (int j = max(0, issued - kVStages); j < issued; ++j)
-          mbar_wait(smem_u32(&bars.v_full[j % kVStages]), (j / kVStages) & 1, &none);
+        for (uint32_t c = vc > kVStages ? vc - kVStages : 0; c < vc; ++c)
+          mbar_wait(smem_u32(&bars.v_full[c % kVStages]), (c / kVStages) & 1, &none);
       }
     }
   } else if (warp == 1) {
@@ -239,61 +281,81 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         return good;
       };
       bool ok = true;
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (n_kv[t] > 0) ok = wait_all(&bars.q_full[t], 0, 3);
-      }
-      for (int j = 0; j <= n_max && ok; ++j) {
-        const int st = j % kKStages;
-        const int jp = j - 1;  // the tile whose P.V is issued in this iteration
-        const int stp = (jp + kVStages) % kVStages;
-        const bool have_k = j < n_max, have_v = jp >= 0;
-        const bool pv0 = have_v && jp < n_kv[0], pv1 = have_v && jp < n_kv[1];
-        // probe everything this iteration needs at once; fall back to a proper wait on a miss
-        const bool k_hit = !have_k || mbar_try_wait(smem_u32(&bars.k_full[st]), (j / kKStages) & 1);
-        const bool v_hit = !have_v || mbar_try_wait(smem_u32(&bars.v_full[stp]), (jp / kVStages) & 1);
-        const bool p0_hit = !pv0 || mbar_try_wait(smem_u32(&bars.p_ready[0]), jp & 1);
-        if (!__all_sync(0xffffffffu, k_hit)) ok = wait_all(&bars.k_full[st], (j / kKStages) & 1, 4);
-        if (ok && !__all_sync(0xffffffffu, v_hit)) ok = wait_all(&bars.v_full[stp], (jp / kVStages) & 1, 5);
-        if (!ok) break;
-        const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
-        const uint64_t vdesc = umma_smem_desc_sw128(sV + stp * kTileBytes, kHalfBytes, 1024);
+      uint32_t kc = 0, vc = 0;      // K / V tiles consumed before this item
+      uint32_t sn[2] = {0, 0};      // tile steps of tile t before this item (parity of s_full, p_ready)
+      uint32_t on[2] = {0, 0};      // items of tile t before this one (parity of q_full, o_free)
+      Item it_;
+      for (int it = 0; it < n_waves && ok; ++it) {
+        if (!get_item(it, p, &it_)) continue;
+        const int n_max = it_.n_max;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (it_.n_kv[t] > 0) ok = wait_all(&bars.q_full[t], on[t] & 1, 3);
+        }
+        for (int j = 0; j <= n_max && ok; ++j) {
+          const int jp = j - 1;  // the tile whose P.V is issued in this iteration
+          const bool have_k = j < n_max, have_v = jp >= 0;
+          const uint32_t kidx = kc + j, vidx = vc + (have_v ? jp : 0);
+          const int st = kidx % kKStages, stp = vidx % kVStages;
+          const bool pv0 = have_v && jp < it_.n_kv[0], pv1 = have_v && jp < it_.n_kv[1];
+          // probe everything this iteration needs at once; fall back to a proper wait on a miss
+          const bool k_hit = !have_k || mbar_try_wait(smem_u32(&bars.k_full[st]), (kidx / kKStages) & 1);
+          const bool v_hit = !have_v || mbar_try_wait(smem_u32(&bars.v_full[stp]), (vidx / kVStages) & 1);
+          const bool p0_hit = !pv0 || mbar_try_wait(smem_u32(&bars.p_ready[0]), (sn[0] + jp) & 1);
+          if (!__all_sync(0xffffffffu, k_hit)) ok = wait_all(&bars.k_full[st], (kidx / kKStages) & 1, 4);
+          if (ok && !__all_sync(0xffffffffu, v_hit)) ok = wait_all(&bars.v_full[stp], (vidx / kVStages) & 1, 5);
+          if (!ok) break;
+          const uint64_t kdesc = umma_smem_desc_sw128(sK + st * kTileBytes, 16, 1024);
+          const uint64_t vdesc = umma_smem_desc_sw128(sV + stp * kTileBytes, kHalfBytes, 1024);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const uint32_t tS = tbase + t * 128;          // S_t, and P_t in its first 64 columns
-          const uint32_t tO = tbase + 256 + t * 128;    // O_t
-          const bool pv = t == 0 ? pv0 : pv1;
-          const bool qk = j < n_kv[t];
-          if (pv) {
-            if (t == 1 || !__all_sync(0xffffffffu, p0_hit)) {
-              ok = wait_all(&bars.p_ready[t], jp & 1, 6);
-              if (!ok) break;
-            }
-          }
-          tc_fence_after_sync();
-          if (elect_one()) {
+          for (int t = 0; t < 2; ++t) {
+            const uint32_t tS = tbase + t * 128;          // S_t, and P_t in its first 64 columns
+            const uint32_t tO = tbase + 256 + t * 128;    // O_t
+            const bool pv = t == 0 ? pv0 : pv1;
+            const bool qk = j < it_.n_kv[t];
             if (pv) {
-#pragma unroll
-              for (int kk = 0; kk < 8; ++kk) {
-                umma_ts(tO, tS + kk * 8, vdesc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
-                        (jp > 0 || kk > 0) ? 1u : 0u);
+              if (t == 1 || !__all_sync(0xffffffffu, p0_hit)) {
+                ok = wait_all(&bars.p_ready[t], (sn[t] + jp) & 1, 6);
+                if (!ok) break;
               }
-              // O_t is complete after its last P.V; the V stage is free after tile 1's P.V
-              if (jp == n_kv[t] - 1) umma_commit(smem_u32(&bars.o_done[t]));
-              if (t == 1 || !pv1) umma_commit(smem_u32(&bars.v_empty[stp]));
-            }
-            if (qk) {
-              const uint64_t qdesc = umma_smem_desc_sw128(sQ + t * kTileBytes, 16, 1024);
-#pragma unroll
-              for (int kk = 0; kk < 8; ++kk) {
-                const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
-                umma_ss(tS, qdesc + off, kdesc + off, idesc_qk, kk > 0 ? 1u : 0u);
+              if (jp == 0 && on[t] > 0) {
+                // the first P.V of an item overwrites O_t: the previous item's epilogue must have read it
+                ok = wait_all(&bars.o_free[t], (on[t] - 1) & 1, 12);
+                if (!ok) break;
               }
-              umma_commit(smem_u32(&bars.s_full[t]));
             }
-            // the K stage is free after the last QK^T that reads it
-            if (qk && (t == 1 || j >= n_kv[1])) umma_commit(smem_u32(&bars.k_empty[st]));
+            tc_fence_after_sync();
+            if (elect_one()) {
+              if (pv) {
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                  umma_ts(tO, tS + kk * 8, vdesc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
+                          (jp > 0 || kk > 0) ? 1u : 0u);
+                }
+                // O_t is complete after its last P.V; the V stage is free after the last P.V reading it
+                if (jp == it_.n_kv[t] - 1) umma_commit(smem_u32(&bars.o_done[t]));
+                if (t == 1 || !pv1) umma_commit(smem_u32(&bars.v_empty[stp]));
+              }
+              if (qk) {
+                const uint64_t qdesc = umma_smem_desc_sw128(sQ + t * kTileBytes, 16, 1024);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                  const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+                  umma_ss(tS, qdesc + off, kdesc + off, idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&bars.s_full[t]));
+                // the K stage is free after the last QK^T that reads it; Q_t after its last QK^T
+                if (t == 1 || j >= it_.n_kv[1]) umma_commit(smem_u32(&bars.k_empty[st]));
+                if (j == it_.n_kv[t] - 1) umma_commit(smem_u32(&bars.q_empty[t]));
+              }
+            }
+            __syncwarp();
           }
-          __syncwarp();
+        }
+        kc += n_max;
+        vc += n_max;
+        for (int t = 0; t < 2; ++t) {
+          sn[t] += it_.n_kv[t];
+          if (it_.n_kv[t] > 0) ++on[t];
         }
       }
     }
@@ -305,166 +367,169 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;                     // TMEM lane quarter this warp may touch
     const int r_in_tile = wq * 32 + lane;
-    const int row = q0[t] + r_in_tile;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const uint32_t tS = tbase + lane_base + t * 128;
     const uint32_t tO = tbase + lane_base + 256 + t * 128;
-    const int n_t = n_kv[t];
     const float scale = p.scale_log2;
-    int lim = p.Skv - 1;
-    if (p.causal) lim = min(lim, row + p.diag_off);
-    const int tile_min_lim = p.causal ? min(p.Skv - 1, q0[t] + p.diag_off) : p.Skv - 1;
-
-    float m_ref = -INFINITY;             // exponent reference of this row (raw logit units)
-    float l = 0.f;                       // row sum under the current reference
     bool ok = true;
+    uint32_t sn = 0;  // tile steps of this tile before the current item
+    uint32_t on = 0;  // items of this tile before the current one
+    Item it_;
+    for (int it = 0; it < n_waves && ok; ++it) {
+      if (!get_item(it, p, &it_)) continue;
+      const int n_t = it_.n_kv[t];
+      if (n_t == 0) continue;
+      const int row = it_.q0[t] + r_in_tile;
+      int lim = p.Skv - 1;
+      if (p.causal) lim = min(lim, row + p.diag_off);
+      const int tile_min_lim = p.causal ? min(p.Skv - 1, it_.q0[t] + p.diag_off) : p.Skv - 1;
 
-    for (int j = 0; j < n_t && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[t]), j & 1, abortp));
-      if (!ok) { if (lane == 0) record_timeout(p.status, 7); break; }
-      tc_fence_after_sync();
-      const bool masked_tile = j * kTile + kTile - 1 > tile_min_lim;
-      const int thr = lim - j * kTile;  // columns > thr of this tile are masked for this row
+      float m_ref = -INFINITY;             // exponent reference of this row (raw logit units)
+      float l = 0.f;                       // row sum under the current reference
 
-      // The whole 128-wide row is exponentiated at once against the reference left by earlier
-      // tiles, so the MUFU starts right after the TMEM load and runs without a gap; the largest
-      // result is looked at afterwards.  If it exceeds 2^8 -- or is not finite, as in the very
-      // first tile, which has no reference yet -- the rare path takes the true maximum, moves the
-      // reference up, rescales what was accumulated under the old one and redoes the tile.
-      float e[128];
-      {
-        uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(e);
-        tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
-        tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
-        tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&u[64]));
-        tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&u[96]));
-        tmem_wait_ld();
-      }
-      if (masked_tile) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i) e[i] = (i > thr) ? -INFINITY : e[i];
-      }
-      {
-        const float neg_m = -m_ref * scale;
-#pragma unroll
-        for (int i = 0; i < 128; ++i) e[i] = ex2(fmaf(e[i], scale, neg_m));
-      }
-      // The tile's row sum doubles as the overflow probe: it bounds every term from above, and it
-      // is NaN or infinite exactly when some term is (first tile: no reference yet).  P is packed
-      // to 16 bits right away (the compiler interleaves it with the exponentials), so that only
-      // the TMEM store is left once the probe has passed.
-      float ts8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        ts8[i & 7] += e[2 * i] + e[2 * i + 1];
-        pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
-      }
-      float tile_sum = ((ts8[0] + ts8[1]) + (ts8[2] + ts8[3])) + ((ts8[4] + ts8[5]) + (ts8[6] + ts8[7]));
-      const bool need = !(tile_sum <= kRescaleLimit);
-      if (__any_sync(0xffffffffu, need)) {
-        // ---- rare: the raw logits are still intact in TMEM; take their maximum, 32 columns at a time
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t u[32];
-          tmem_ld32(tS + c * 32, u);
+      for (int j = 0; j < n_t && ok; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[t]), (sn + j) & 1, abortp));
+        if (!ok) { if (lane == 0) record_timeout(p.status, 7); break; }
+        tc_fence_after_sync();
+        const bool masked_tile = j * kTile + kTile - 1 > tile_min_lim;
+        const int thr = lim - j * kTile;  // columns > thr of this tile are masked for this row
+
+        // The whole 128-wide row is exponentiated at once against the reference left by earlier
+        // tiles, so the MUFU starts right after the TMEM load and runs without a gap; the largest
+        // result is looked at afterwards.  If it exceeds 2^8 -- or is not finite, as in the very
+        // first tile, which has no reference yet -- the rare path takes the true maximum, moves the
+        // reference up, rescales what was accumulated under the old one and redoes the tile.
+        float e[128];
+        {
+          uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(e);
+          tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
+          tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
+          tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&u[64]));
+          tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&u[96]));
           tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
-            mx = fmaxf(mx, v);
-          }
         }
-        float alpha = 1.f;
-        if (need) {
-          alpha = ex2((m_ref - mx) * scale);  // 0 when there was no reference yet
-          m_ref = mx;
-          l *= alpha;
+        if (masked_tile) {
+  #pragma unroll
+          for (int i = 0; i < 128; ++i) e[i] = (i > thr) ? -INFINITY : e[i];
         }
-        if (j > 0) {
-          // O_t is the sum over earlier tiles.  P.V of tile j-1 was issued before QK^T of tile j
-          // and the tensor pipe retires in order, so S_t(j) being ready means O_t is complete.
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tO + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + c * 32, o);
-          }
-          tmem_wait_st();
+        {
+          const float neg_m = -m_ref * scale;
+  #pragma unroll
+          for (int i = 0; i < 128; ++i) e[i] = ex2(fmaf(e[i], scale, neg_m));
         }
-        const float neg_m = -m_ref * scale;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t u[32];
-          tmem_ld32(tS + c * 32, u);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
-            e[c * 32 + i] = ex2(fmaf(v, scale, neg_m));
-          }
-        }
-        tile_sum = 0.f;
-#pragma unroll
+        // The tile's row sum doubles as the overflow probe: it bounds every term from above, and it
+        // is NaN or infinite exactly when some term is (first tile: no reference yet).  P is packed
+        // to 16 bits right away (the compiler interleaves it with the exponentials), so that only
+        // the TMEM store is left once the probe has passed.
+        float ts8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[64];
+  #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          tile_sum += e[2 * i] + e[2 * i + 1];
+          ts8[i & 7] += e[2 * i] + e[2 * i + 1];
           pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
         }
+        float tile_sum = ((ts8[0] + ts8[1]) + (ts8[2] + ts8[3])) + ((ts8[4] + ts8[5]) + (ts8[6] + ts8[7]));
+        const bool need = !(tile_sum <= kRescaleLimit);
+        if (__any_sync(0xffffffffu, need)) {
+          // ---- rare: the raw logits are still intact in TMEM; take their maximum, 32 columns at a time
+          float mx = -INFINITY;
+  #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t u[32];
+            tmem_ld32(tS + c * 32, u);
+            tmem_wait_ld();
+  #pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
+              mx = fmaxf(mx, v);
+            }
+          }
+          float alpha = 1.f;
+          if (need) {
+            alpha = ex2((m_ref - mx) * scale);  // 0 when there was no reference yet
+            m_ref = mx;
+            l *= alpha;
+          }
+          if (j > 0) {
+            // O_t is the sum over earlier tiles of this work item.  P.V of tile j-1 was issued before
+            // QK^T of tile j and the tensor pipe retires in order, so S_t(j) being ready means O_t is
+            // complete.
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO + c * 32, o);
+              tmem_wait_ld();
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + c * 32, o);
+            }
+            tmem_wait_st();
+          }
+          const float neg_m = -m_ref * scale;
+  #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t u[32];
+            tmem_ld32(tS + c * 32, u);
+            tmem_wait_ld();
+  #pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
+              e[c * 32 + i] = ex2(fmaf(v, scale, neg_m));
+            }
+          }
+          tile_sum = 0.f;
+  #pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            tile_sum += e[2 * i] + e[2 * i + 1];
+            pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
+          }
+        }
+        l += tile_sum;
+        tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+        tmem_st32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+        if (!ok) break;
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bars.p_ready[t]));
       }
-      l += tile_sum;
-      tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
-      tmem_st32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
       if (!ok) break;
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bars.p_ready[t]));
-    }
 
-    if (ok && n_t > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), 0, abortp));  // committed once, after the last P.V
-      if (!ok && lane == 0) record_timeout(p.status, 9);
-    }
-    if (ok && n_t > 0) {
+      // ---- epilogue of the item: O_t / l straight from TMEM to global memory
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), on & 1, abortp));
+      if (!ok) { if (lane == 0) record_timeout(p.status, 9); break; }
       tc_fence_after_sync();
-      const float inv_l = 1.f / l;
-      // Q_t is dead once the last P.V has completed: stage O_t there in the TMA store layout
-      uint8_t* stage = smem_gen + t * kTileBytes;
+      {
+        const float inv_l = 1.f / l;
+        uint16_t* orow = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(it_.b) * p.o_sb +
+                         static_cast<int64_t>(row) * p.o_ss + static_cast<int64_t>(it_.h) * p.o_sh;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tO + c * 32, o);
-        tmem_wait_ld();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
+          tmem_wait_ld();
+          if (c == 3) {
+            // O_t is in registers: the next item's first P.V may overwrite it
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars.o_free[t]));
+          }
+          if (row < p.Sq) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 v;
-          v.x = pack2<kBF16>(__uint_as_float(o[g * 8 + 0]) * inv_l, __uint_as_float(o[g * 8 + 1]) * inv_l);
-          v.y = pack2<kBF16>(__uint_as_float(o[g * 8 + 2]) * inv_l, __uint_as_float(o[g * 8 + 3]) * inv_l);
-          v.z = pack2<kBF16>(__uint_as_float(o[g * 8 + 4]) * inv_l, __uint_as_float(o[g * 8 + 5]) * inv_l);
-          v.w = pack2<kBF16>(__uint_as_float(o[g * 8 + 6]) * inv_l, __uint_as_float(o[g * 8 + 7]) * inv_l);
-          const int chunk = c * 4 + g;  // 16-byte chunk of the 256-byte row
-          *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes +
-                                    sw128_offset(r_in_tile, chunk & 7)) = v;
+            for (int g = 0; g < 4; ++g) {
+              uint4 v;
+              v.x = pack2<kBF16>(__uint_as_float(o[g * 8 + 0]) * inv_l, __uint_as_float(o[g * 8 + 1]) * inv_l);
+              v.y = pack2<kBF16>(__uint_as_float(o[g * 8 + 2]) * inv_l, __uint_as_float(o[g * 8 + 3]) * inv_l);
+              v.z = pack2<kBF16>(__uint_as_float(o[g * 8 + 4]) * inv_l, __uint_as_float(o[g * 8 + 5]) * inv_l);
+              v.w = pack2<kBF16>(__uint_as_float(o[g * 8 + 6]) * inv_l, __uint_as_float(o[g * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+            }
+          }
+        }
+        if (p.lse2 != nullptr && row < p.Sq) {
+          p.lse2[(static_cast<size_t>(it_.b) * p.H + it_.h) * p.Sq + row] = m_ref * scale + log2f(l);
         }
       }
-      if (p.lse2 != nullptr && row < p.Sq) {
-        p.lse2[(static_cast<size_t>(b) * p.H + h) * p.Sq + row] = m_ref * scale + log2f(l);
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&bars.epi[t]));
-      if (r_in_tile == 0) {
-        if (mbar_wait(smem_u32(&bars.epi[t]), 0, abortp)) {
-          tma_store_4d(&map_o, sQ + t * kTileBytes, 0, h, q0[t], b);
-          tma_store_4d(&map_o, sQ + t * kTileBytes + kHalfBytes, 64, h, q0[t], b);
-          tma_store_commit();
-          tma_store_wait_read();
-        } else {
-          record_timeout(p.status, 10);
-        }
-      }
+      sn += n_t;
+      ++on;
     }
   }
 
@@ -479,8 +544,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 }  // namespace
 
 cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                            const CUtensorMap& mo, float* lse2, const AttnShape& s,
-                            cudaStream_t stream) {
+                            void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, float* lse2,
+                            const AttnShape& s, int num_sms, cudaStream_t stream) {
   FwdParams p;
   p.B = s.B;
   p.H = s.H;
@@ -489,14 +554,19 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.causal = s.causal;
   p.diag_off = s.Skv - s.Sq;
   p.nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
+  p.n_items = p.nq_blocks * s.B * s.H;
   p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
   p.lse2 = lse2;
+  p.out = out;
+  p.o_sb = o_sb;
+  p.o_ss = o_ss;
+  p.o_sh = o_sh;
   p.status = device_status_words();
-  const dim3 grid(static_cast<unsigned>(p.nq_blocks) * s.B * s.H);
+  const dim3 grid(static_cast<unsigned>(p.n_items < num_sms ? p.n_items : num_sms));
   auto kern = s.bf16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, mo, p);
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
   count_launch();
   return cudaPeekAtLastError();
 }

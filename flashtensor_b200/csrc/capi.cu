@@ -48,6 +48,19 @@ int check_arch() {
   return cached[dev] == 10 ? ASUKA_OK : ASUKA_ERR_UNSUPPORTED_ARCH;
 }
 
+// multiprocessor count of the current device (the persistent kernels launch one CTA per SM)
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 bool is_16bit(int dt) { return dt == ASUKA_F16 || dt == ASUKA_BF16; }
 
 // [B,S,H,128] 16-bit tensor usable as a TMA source/destination
@@ -132,11 +145,12 @@ int attn_fwd_impl(const asuka_attn_params* p, float* lse_override, cudaStream_t 
     lse = static_cast<float*>(p->lse.ptr);
   }
   if ((r = check_arch()) != ASUKA_OK) return r;
-  CUtensorMap mq, mk, mv, mo;
-  if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k)) || (r = make_map(&mv, p->v)) ||
-      (r = make_map(&mo, p->out)))
-    return r;
-  return map_cuda(launch_attn_fwd(mq, mk, mv, mo, lse, c.s, stream));
+  CUtensorMap mq, mk, mv;
+  if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k)) || (r = make_map(&mv, p->v))) return r;
+  const int sms = sm_count();
+  if (sms <= 0) return ASUKA_ERR_CUDA;
+  return map_cuda(launch_attn_fwd(mq, mk, mv, p->out.ptr, p->out.stride[0], p->out.stride[1],
+                                  p->out.stride[2], lse, c.s, sms, stream));
 }
 
 

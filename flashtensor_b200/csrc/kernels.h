@@ -19,10 +19,11 @@ struct AttnShape {
   bool bf16;
 };
 
-// q/k/v/out tensor maps: [B,S,H,128] boxes of 64 x 1 x 128 x 1, 128-byte swizzle.
+// q/k/v tensor maps: [B,S,H,128] boxes of 64 x 1 x 128 x 1, 128-byte swizzle.  `out` is written
+// with plain 16-byte stores (strides in elements).  `num_sms` sizes the persistent grid.
 cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                            const CUtensorMap& mo, float* lse2, const AttnShape& s,
-                            cudaStream_t stream);
+                            void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, float* lse2,
+                            const AttnShape& s, int num_sms, cudaStream_t stream);
 
 struct ScoreArgs {
   const float* lse2;       // [B,H,Sq]
