@@ -8,9 +8,9 @@ import os
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG_DIR, "libasuka_b200.so")
 
-F16, BF16, F32, I32 = 0, 1, 2, 3
+F16, BF16, F32, I32, U8 = 0, 1, 2, 3, 4
 
-SCORE_SUM, SCORE_SUM_SQ, SCORE_PERTURBED = 0, 1, 2
+SCORE_SUM, SCORE_SUM_SQ, SCORE_PERTURBED, SCORE_CORM = 0, 1, 2, 3
 SELECT_TOPK, SELECT_TOPK_RECENT, SELECT_ROCO = 0, 1, 2
 
 STATUS_NAMES = {
@@ -28,13 +28,15 @@ class Tensor(ctypes.Structure):
 
 class AttnParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor), ("lse", Tensor),
-              ("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32)]
+              ("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32),
+              ("softcap", ctypes.c_float)]
 
 
 class ScoreParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("lse", Tensor), ("score", Tensor), ("score_sq", Tensor),
               ("exp_rand", Tensor), ("softmax_scale", ctypes.c_float), ("tau", ctypes.c_float),
-              ("seed", ctypes.c_uint64), ("causal", ctypes.c_int32), ("mode", ctypes.c_int32)]
+              ("seed", ctypes.c_uint64), ("causal", ctypes.c_int32), ("mode", ctypes.c_int32),
+              ("corm_mask", Tensor)]
 
 
 class SelectParams(ctypes.Structure):
@@ -69,6 +71,7 @@ SYMBOLS = {
     "asuka_b200_col_scores": (ctypes.c_int, [ctypes.POINTER(ScoreParams), ctypes.c_void_p]),
     "asuka_b200_keyformer_rowstat": (ctypes.c_int, [ctypes.POINTER(ScoreParams), ctypes.c_void_p]),
     "asuka_b200_select_topk": (ctypes.c_int, [ctypes.POINTER(SelectParams), ctypes.c_void_p]),
+    "asuka_b200_pool_scores": (ctypes.c_int, [ctypes.POINTER(Tensor), ctypes.POINTER(Tensor), ctypes.c_int32, ctypes.c_void_p]),
     "asuka_b200_sima_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_sima_fwd": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_case_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.POINTER(ctypes.c_size_t)]),

@@ -38,7 +38,7 @@ class B200Builder(Builder):
 
   def build_callable(self) -> Callable[..., Any]:
     model = cases.CASES[self.case_name](**self.case_kwargs)
-    n_in = 4 if self.case_name == "KeyFormer" else 3
+    n_in = 4 if self.case_name in ("KeyFormer", "Corm") else 3
     check = self.check_before_run
 
     def f(*args):

@@ -68,6 +68,20 @@ class Attn(_Case):
     return ops.attn_fwd(q, k, v, causal=self.causal)
 
 
+class Gemma2(_Case):
+  """cases/kernels/gemma2.py: attention with soft-capped logits, cap * tanh(logits / cap)."""
+  output_names = ["out"]
+
+  def __init__(self, logit_softcapping=50.0, kv_head_num=32, head_num=32, head_dim=128, causal=True):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.logit_softcapping = logit_softcapping
+    self.causal = causal
+
+  def forward(self, q, k, v):
+    self._check(q)
+    return ops.attn_fwd(q, k, v, causal=self.causal, softcap=self.logit_softcapping)
+
+
 class H2O(_Case):
   """cases/kernels/h2o.py:7-38: returns (out, h2o_score [B,H,Skv] f32)."""
   output_names = ["out", "h2o_score"]
@@ -85,6 +99,46 @@ class H2O(_Case):
     `recent` keys."""
     self._check(q)
     return ops.h2o(q, k, v, causal=self.causal, k_keep=k_keep, recent=recent)
+
+
+class SnapKV(_Case):
+  """cases/kernels/snapkv.py: (out, snapkv_score), the H2O column sums smoothed by a moving
+  average of `kernel_size` keys."""
+  output_names = ["out", "snapkv_score"]
+
+  def __init__(self, kernel_size=5, kv_head_num=32, head_num=32, head_dim=128, causal=True):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.kernel_size = kernel_size
+    self.causal = causal
+
+  def forward(self, q, k, v):
+    self._check(q)
+    out, score = ops.h2o(q, k, v, causal=self.causal)
+    return out, ops.pool_scores(score, self.kernel_size)
+
+
+class Corm(_Case):
+  """cases/kernels/corm.py: (out, corm_score) with corm_score[b,h,j] = any_i(p_ij >= corm_mask[i,j])."""
+  output_names = ["out", "corm_score"]
+
+  def __init__(self, kv_head_num=32, head_num=32, head_dim=128, causal=True):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.causal = causal
+
+  def forward(self, q, k, v, corm_mask):
+    self._check(q)
+    out, lse = ops.attn_fwd(q, k, v, causal=self.causal, return_lse=True)
+    from . import _lib
+    keep = ops.col_scores(q, k, lse, mode=_lib.SCORE_CORM, causal=self.causal, corm_mask=corm_mask)
+    return out, keep
+
+  def prepare(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):
+    ret = super().prepare(batch_size, q_len, kv_len, dtype, device)
+    dev = ret["input"]["q"].device
+    # row i of the threshold is 1 / (i + 1), cases/kernels/corm.py:46-48
+    rows = 1.0 / torch.arange(1, q_len + 1, dtype=torch.float32, device=dev)
+    ret["input"]["corm_mask"] = rows[:, None].expand(q_len, kv_len).contiguous()
+    return ret
 
 
 class KeyFormer(_Case):
@@ -153,7 +207,7 @@ class SimA(_Case):
     return ret
 
 
-CASES = {"Attn": Attn, "H2O": H2O, "KeyFormer": KeyFormer, "RoCo": RoCo, "SimA": SimA}
+CASES = {"Attn": Attn, "Gemma2": Gemma2, "SnapKV": SnapKV, "Corm": Corm, "H2O": H2O, "KeyFormer": KeyFormer, "RoCo": RoCo, "SimA": SimA}
 
 
 def get_model(name="H2O", **kwargs):

@@ -47,7 +47,8 @@ struct FwdParams {
   int B, H, Sq, Skv;
   int causal, diag_off;
   int nq_blocks, n_items;
-  float scale_log2;
+  float scale_log2;          // softmax_scale * log2(e)
+  float cap_in, cap_out;     // soft-capping: softmax_scale / cap and cap * log2(e)
   float* lse2;
   void* out;                 // [B, Sq, H, 128], 16-bit, strides in elements
   int64_t o_sb, o_ss, o_sh;
@@ -64,6 +65,12 @@ struct Bars {
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
@@ -135,7 +142,9 @@ __device__ __forceinline__ int item_waves(const FwdParams& p) {
   return (p.n_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 }
 
-template <bool kBF16>
+// kCap: Gemma-2 style soft-capping, logits -> cap * tanh(logits / cap) before the mask
+// (cases/kernels/gemma2.py:30-33; the reference emits tanh.approx.f32 too, to_triton.cpp:351-369).
+template <bool kBF16, bool kCap>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
@@ -384,7 +393,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (p.causal) lim = min(lim, row + p.diag_off);
       const int tile_min_lim = p.causal ? min(p.Skv - 1, it_.q0[t] + p.diag_off) : p.Skv - 1;
 
-      float m_ref = -INFINITY;             // exponent reference of this row (raw logit units)
+      float m_ref = -INFINITY;             // exponent reference of this row, in log2 units of the scaled logit
       float l = 0.f;                       // row sum under the current reference
 
       for (int j = 0; j < n_t && ok; ++j) {
@@ -396,8 +405,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
         // The whole 128-wide row is exponentiated at once against the reference left by earlier
         // tiles, so the MUFU starts right after the TMEM load and runs without a gap; the largest
-        // result is looked at afterwards.  If it exceeds 2^8 -- or is not finite, as in the very
-        // first tile, which has no reference yet -- the rare path takes the true maximum, moves the
+        // tile's row sum is looked at afterwards.  If it exceeds 2^13 -- or is not finite, as in the
+        // very first tile, which has no reference yet -- the rare path takes the true maximum, moves the
         // reference up, rescales what was accumulated under the old one and redoes the tile.
         float e[128];
         {
@@ -408,14 +417,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&u[96]));
           tmem_wait_ld();
         }
+        if constexpr (kCap) {
+          // cap first, mask afterwards (the reference adds the mask to the capped logits)
+#pragma unroll
+          for (int i = 0; i < 128; ++i) e[i] = tanh_approx(e[i] * p.cap_in);
+        }
         if (masked_tile) {
-  #pragma unroll
+#pragma unroll
           for (int i = 0; i < 128; ++i) e[i] = (i > thr) ? -INFINITY : e[i];
         }
         {
-          const float neg_m = -m_ref * scale;
-  #pragma unroll
-          for (int i = 0; i < 128; ++i) e[i] = ex2(fmaf(e[i], scale, neg_m));
+          const float mul = kCap ? p.cap_out : scale;
+          const float neg_m = -m_ref;
+#pragma unroll
+          for (int i = 0; i < 128; ++i) e[i] = ex2(fmaf(e[i], mul, neg_m));
         }
         // The tile's row sum doubles as the overflow probe: it bounds every term from above, and it
         // is NaN or infinite exactly when some term is (first tile: no reference yet).  P is packed
@@ -423,7 +438,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // the TMEM store is left once the probe has passed.
         float ts8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         uint32_t pk[64];
-  #pragma unroll
+#pragma unroll
         for (int i = 0; i < 64; ++i) {
           ts8[i & 7] += e[2 * i] + e[2 * i + 1];
           pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
@@ -433,52 +448,57 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (__any_sync(0xffffffffu, need)) {
           // ---- rare: the raw logits are still intact in TMEM; take their maximum, 32 columns at a time
           float mx = -INFINITY;
-  #pragma unroll
+#pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t u[32];
             tmem_ld32(tS + c * 32, u);
             tmem_wait_ld();
-  #pragma unroll
+#pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
               mx = fmaxf(mx, v);
             }
           }
+          // the scaled (and capped) logit is monotone in the raw one: transform the maximum
+          const float mx2 = kCap ? tanh_approx(mx * p.cap_in) * p.cap_out : mx * scale;
           float alpha = 1.f;
           if (need) {
-            alpha = ex2((m_ref - mx) * scale);  // 0 when there was no reference yet
-            m_ref = mx;
+            alpha = ex2(m_ref - mx2);  // 0 when there was no reference yet
+            m_ref = mx2;
             l *= alpha;
           }
           if (j > 0) {
             // O_t is the sum over earlier tiles of this work item.  P.V of tile j-1 was issued before
             // QK^T of tile j and the tensor pipe retires in order, so S_t(j) being ready means O_t is
             // complete.
-  #pragma unroll
+#pragma unroll
             for (int c = 0; c < 4; ++c) {
               uint32_t o[32];
               tmem_ld32(tO + c * 32, o);
               tmem_wait_ld();
-  #pragma unroll
+#pragma unroll
               for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
               tmem_st32(tO + c * 32, o);
             }
             tmem_wait_st();
           }
-          const float neg_m = -m_ref * scale;
-  #pragma unroll
+          const float mul = kCap ? p.cap_out : scale;
+          const float neg_m = -m_ref;
+#pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t u[32];
             tmem_ld32(tS + c * 32, u);
             tmem_wait_ld();
-  #pragma unroll
+#pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const float v = (masked_tile && c * 32 + i > thr) ? -INFINITY : __uint_as_float(u[i]);
-              e[c * 32 + i] = ex2(fmaf(v, scale, neg_m));
+              float v = __uint_as_float(u[i]);
+              if constexpr (kCap) v = tanh_approx(v * p.cap_in);
+              v = (masked_tile && c * 32 + i > thr) ? -INFINITY : v;
+              e[c * 32 + i] = ex2(fmaf(v, mul, neg_m));
             }
           }
           tile_sum = 0.f;
-  #pragma unroll
+#pragma unroll
           for (int i = 0; i < 64; ++i) {
             tile_sum += e[2 * i] + e[2 * i + 1];
             pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
@@ -525,7 +545,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
         if (p.lse2 != nullptr && row < p.Sq) {
-          p.lse2[(static_cast<size_t>(it_.b) * p.H + it_.h) * p.Sq + row] = m_ref * scale + log2f(l);
+          p.lse2[(static_cast<size_t>(it_.b) * p.H + it_.h) * p.Sq + row] = m_ref + log2f(l);
         }
       }
       sn += n_t;
@@ -556,6 +576,8 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
   p.n_items = p.nq_blocks * s.B * s.H;
   p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+  p.cap_in = s.softcap > 0.f ? s.softmax_scale / s.softcap : 0.f;
+  p.cap_out = s.softcap * 1.4426950408889634f;
   p.lse2 = lse2;
   p.out = out;
   p.o_sb = o_sb;
@@ -563,8 +585,10 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.o_sh = o_sh;
   p.status = device_status_words();
   const dim3 grid(static_cast<unsigned>(p.n_items < num_sms ? p.n_items : num_sms));
-  auto kern = s.bf16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, FwdParams);
+  if (s.softcap > 0.f) kern = s.bf16 ? attn_fwd_kernel<true, true> : attn_fwd_kernel<false, true>;
+  else kern = s.bf16 ? attn_fwd_kernel<true, false> : attn_fwd_kernel<false, false>;
+  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (e != cudaSuccess) return e;
   kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
   count_launch();

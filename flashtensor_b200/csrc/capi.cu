@@ -28,6 +28,22 @@ uint32_t* device_status_words() {
 }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  struct Entry { const void* k; int dev; int bytes; };
+  static std::mutex mu;
+  static Entry seen[256];
+  static int n_seen = 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i].k == kernel && seen[i].dev == dev && seen[i].bytes >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && n_seen < 256) seen[n_seen++] = Entry{kernel, dev, bytes};
+  return e;
+}
+
 namespace {
 
 constexpr int kHeadDim = 128;
@@ -122,6 +138,7 @@ int check_qk(const asuka_tensor& q, const asuka_tensor& k, float scale, int caus
   o->s.Skv = static_cast<int>(k.shape[1]);
   o->s.causal = causal ? 1 : 0;
   o->s.softmax_scale = scale > 0.f ? scale : 1.0f / std::sqrt(static_cast<float>(kHeadDim));
+  o->s.softcap = 0.f;
   o->s.bf16 = q.dtype == ASUKA_BF16;
   return ASUKA_OK;
 }
@@ -138,6 +155,8 @@ int attn_fwd_impl(const asuka_attn_params* p, float* lse_override, cudaStream_t 
   for (int i = 0; i < 4; ++i) {
     if (p->v.shape[i] != p->k.shape[i] || p->out.shape[i] != p->q.shape[i]) return ASUKA_ERR_BAD_SHAPE;
   }
+  if (std::isnan(p->softcap) || std::isinf(p->softcap) || p->softcap < 0.f) return ASUKA_ERR_BAD_ARGUMENT;
+  c.s.softcap = p->softcap;
   float* lse = lse_override;
   if (lse == nullptr && p->lse.ptr != nullptr) {
     const int64_t shp[3] = {c.s.B, c.s.H, c.s.Sq};
@@ -171,7 +190,8 @@ int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a)
   if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
   int r;
   if ((r = check_qk(p->q, p->k, p->softmax_scale, p->causal, c)) != ASUKA_OK) return r;
-  if (p->mode != ASUKA_SCORE_SUM && p->mode != ASUKA_SCORE_SUM_SQ && p->mode != ASUKA_SCORE_PERTURBED)
+  if (p->mode != ASUKA_SCORE_SUM && p->mode != ASUKA_SCORE_SUM_SQ && p->mode != ASUKA_SCORE_PERTURBED &&
+      p->mode != ASUKA_SCORE_CORM)
     return ASUKA_ERR_BAD_ARGUMENT;
   const int64_t lshape[3] = {c->s.B, c->s.H, c->s.Sq};
   const int64_t sshape[3] = {c->s.B, c->s.H, c->s.Skv};
@@ -181,8 +201,20 @@ int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a)
   a->lse2 = static_cast<const float*>(p->lse.ptr);
   a->tau = 1.f;
   if (!rowstat) {
-    if ((r = check_dense(p->score, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
+    if ((r = check_dense(p->score, p->mode == ASUKA_SCORE_CORM ? ASUKA_U8 : ASUKA_F32, 3, sshape)) != ASUKA_OK)
+      return r;
     a->score = static_cast<float*>(p->score.ptr);
+    if (p->mode == ASUKA_SCORE_CORM) {
+      const asuka_tensor& m = p->corm_mask;
+      if (m.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
+      if (m.dtype != ASUKA_F32) return ASUKA_ERR_BAD_DTYPE;
+      if (m.ndim != 2 || m.shape[0] != c->s.Sq || m.shape[1] != c->s.Skv) return ASUKA_ERR_BAD_SHAPE;
+      if (m.stride[1] != 1 || m.stride[0] < 0) return ASUKA_ERR_BAD_STRIDE;
+      a->exp_rand = static_cast<const float*>(m.ptr);  // read like the noise operand, shared by b and h
+      a->er_stride_b = 0;
+      a->er_stride_h = 0;
+      a->er_stride_q = m.stride[0];
+    }
     if (p->mode == ASUKA_SCORE_SUM_SQ) {
       if ((r = check_dense(p->score_sq, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
       a->score_sq = static_cast<float*>(p->score_sq.ptr);
@@ -490,6 +522,26 @@ int asuka_b200_keyformer_rowstat(const asuka_score_params* p, asuka_stream strea
 
 int asuka_b200_select_topk(const asuka_select_params* p, asuka_stream stream) {
   return select_impl(p, static_cast<cudaStream_t>(stream));
+}
+
+int asuka_b200_pool_scores(const asuka_tensor* score, const asuka_tensor* out, int32_t kernel_size,
+                           asuka_stream stream) {
+  if (score == nullptr || out == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (score->ptr == nullptr || out->ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (score->ndim != 3) return ASUKA_ERR_BAD_SHAPE;
+  const int64_t shp[3] = {score->shape[0], score->shape[1], score->shape[2]};
+  for (int i = 0; i < 3; ++i)
+    if (shp[i] <= 0) return ASUKA_ERR_BAD_SHAPE;
+  int r;
+  if ((r = check_dense(*score, ASUKA_F32, 3, shp)) != ASUKA_OK) return r;
+  if ((r = check_dense(*out, ASUKA_F32, 3, shp)) != ASUKA_OK) return r;
+  if (kernel_size < 1 || (kernel_size % 2) == 0 || kernel_size > 1025) return ASUKA_ERR_BAD_ARGUMENT;
+  if (shp[0] * shp[1] > 65535 || shp[2] > (1 << 24)) return ASUKA_ERR_TOO_LARGE;
+  if (out->ptr == score->ptr) return ASUKA_ERR_BAD_ARGUMENT;
+  if ((r = check_arch()) != ASUKA_OK) return r;
+  return map_cuda(launch_pool_scores(static_cast<const float*>(score->ptr), static_cast<float*>(out->ptr),
+                                     static_cast<int>(shp[0] * shp[1]), static_cast<int>(shp[2]),
+                                     kernel_size, static_cast<cudaStream_t>(stream)));
 }
 
 int asuka_b200_sima_workspace_bytes(const asuka_sima_params* p, size_t* bytes) {

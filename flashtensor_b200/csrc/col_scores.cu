@@ -101,7 +101,8 @@ __device__ __forceinline__ void record_timeout(uint32_t* status, uint32_t site) 
   status[1] = site;
 }
 
-// kMode: 0 sum, 1 sum + sum of squares, 2 perturbed (noise operand), 3 perturbed (seeded noise)
+// kMode: 0 sum, 1 sum + sum of squares, 2 perturbed (noise operand), 3 perturbed (seeded noise),
+//        4 CORM: any_i(p_ij >= mask_ij) with a [Sq, Skv] threshold operand (cases/kernels/corm.py:34-37)
 template <bool kBF16, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -265,10 +266,11 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     bool ok = true;
     const uint32_t head_key = kMode == 3 ? seeded_head_key(p.seed, static_cast<uint32_t>(bh)) : 0u;
     const float* er_col = nullptr;
-    if constexpr (kMode == 2) {
+    if constexpr (kMode == 2 || kMode == 4) {  // mode 4: the threshold operand, strides 0 for b and h
       er_col = p.exp_rand + static_cast<int64_t>(b) * p.er_sb + static_cast<int64_t>(h) * p.er_sh +
                min(key, p.Skv - 1);
     }
+    bool hit = false;
 
     if (active[t]) {
       for (int i = i_begin; i < p.nq_tiles; ++i) {
@@ -298,8 +300,8 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
               tmem_ld32(tS + hc * 64, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
               tmem_ld32(tS + hc * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
             }
-            float noise[kMode == 2 ? 64 : 1];
-            if constexpr (kMode == 2) {
+            float noise[(kMode == 2 || kMode == 4) ? 64 : 1];
+            if constexpr (kMode == 2 || kMode == 4) {
 #pragma unroll
               for (int e = 0; e < 64; ++e) {
                 const int qi = min(i * kTile + hc * 64 + e, p.Sq - 1);
@@ -336,10 +338,16 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
               for (int cc = 0; cc < 64; ++cc) s[cc] = (hc * 64 + cc < first_visible) ? 0.f : s[cc];
             }
+            if constexpr (kMode == 4) {
 #pragma unroll
-            for (int cc = 0; cc < 64; ++cc) {
-              acc[cc & 3] += s[cc];
-              if constexpr (kMode == 1) acc2[cc & 3] = fmaf(s[cc], s[cc], acc2[cc & 3]);
+              for (int cc = 0; cc < 64; ++cc)
+                hit = hit || (s[cc] >= noise[cc] && i * kTile + hc * 64 + cc < p.Sq);
+            } else {
+#pragma unroll
+              for (int cc = 0; cc < 64; ++cc) {
+                acc[cc & 3] += s[cc];
+                if constexpr (kMode == 1) acc2[cc & 3] = fmaf(s[cc], s[cc], acc2[cc & 3]);
+              }
             }
           }
         }
@@ -348,7 +356,11 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       if (ok && key < p.Skv) {
         const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
-        p.score[o] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        if constexpr (kMode == 4) {
+          reinterpret_cast<uint8_t*>(p.score)[o] = hit ? 1 : 0;
+        } else {
+          p.score[o] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        }
         if constexpr (kMode == 1) p.score_sq[o] = (acc2[0] + acc2[1]) + (acc2[2] + acc2[3]);
       }
     }
@@ -619,9 +631,10 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
   void (*kern)(CUtensorMap, CUtensorMap, ColParams) = nullptr;
   if (a.mode == ASUKA_SCORE_SUM) kern = s.bf16 ? col_scores_kernel<true, 0> : col_scores_kernel<false, 0>;
   else if (a.mode == ASUKA_SCORE_SUM_SQ) kern = s.bf16 ? col_scores_kernel<true, 1> : col_scores_kernel<false, 1>;
+  else if (a.mode == ASUKA_SCORE_CORM) kern = s.bf16 ? col_scores_kernel<true, 4> : col_scores_kernel<false, 4>;
   else if (a.exp_rand != nullptr) kern = s.bf16 ? col_scores_kernel<true, 2> : col_scores_kernel<false, 2>;
   else kern = s.bf16 ? col_scores_kernel<true, 3> : col_scores_kernel<false, 3>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (e != cudaSuccess) return e;
   kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, p);
   count_launch();
@@ -635,7 +648,7 @@ cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, cons
   cudaError_t e;
   if (a.exp_rand == nullptr) {
     auto kern = s.bf16 ? kf_rowstat_kernel<true, 2> : kf_rowstat_kernel<false, 2>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<2>::kSmem);
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), RsCfg<2>::kSmem);
     if (e != cudaSuccess) return e;
     kern<<<grid, kRsThreads, RsCfg<2>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
     count_launch();
@@ -654,12 +667,12 @@ cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, cons
     const uint32_t box[4] = {32, 128, 1, 1};
     if (tma_host::make_f32_map_sw128(&mn, a.exp_rand, dims, strides, box) != 0) return cudaErrorInvalidValue;
     auto kern = s.bf16 ? kf_rowstat_kernel<true, 1> : kf_rowstat_kernel<false, 1>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<1>::kSmem);
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), RsCfg<1>::kSmem);
     if (e != cudaSuccess) return e;
     kern<<<grid, kRsThreads, RsCfg<1>::kSmem, stream>>>(mq, mk, mn, p, lse2_out);
   } else {
     auto kern = s.bf16 ? kf_rowstat_kernel<true, 0> : kf_rowstat_kernel<false, 0>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<0>::kSmem);
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), RsCfg<0>::kSmem);
     if (e != cudaSuccess) return e;
     kern<<<grid, kRsThreads, RsCfg<0>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
   }

@@ -11,11 +11,14 @@ namespace asuka {
 // Device-side record of bounded waits that expired: word 0 = count, word 1 = last site id.
 uint32_t* device_status_words();  // device address of a 4-word __device__ array
 void count_launch();
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of per call
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 
 struct AttnShape {
   int B, H, Sq, Skv;
   int causal;
   float softmax_scale;
+  float softcap;  // > 0: logits -> softcap * tanh(logits / softcap) before the mask; 0: off
   bool bf16;
 };
 
@@ -48,6 +51,10 @@ struct SelectArgs {
   int rows, S, k_keep, recent, q_len, mode;
 };
 cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream);
+
+// moving average over the key axis of [rows, S] scores (odd kernel size, zero padding)
+cudaError_t launch_pool_scores(const float* in, float* out, int rows, int S, int ksize,
+                               cudaStream_t stream);
 
 struct SimaShape {
   int B, H, S;

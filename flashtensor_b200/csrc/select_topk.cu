@@ -170,13 +170,11 @@ cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(a.S) * (wide ? 8 : 4);
   cudaError_t e;
   if (wide) {
-    e = cudaFuncSetAttribute(select_kernel<uint64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(select_kernel<uint64_t>), static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     select_kernel<uint64_t><<<a.rows, kSelThreads, smem, stream>>>(a);
   } else {
-    e = cudaFuncSetAttribute(select_kernel<uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(select_kernel<uint32_t>), static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     select_kernel<uint32_t><<<a.rows, kSelThreads, smem, stream>>>(a);
   }

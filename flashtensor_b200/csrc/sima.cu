@@ -573,7 +573,7 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   cudaError_t e;
   {
     auto kern = s.bf16 ? sima_stats_kernel<true> : sima_stats_kernel<false>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmem);
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kStSmem);
     if (e != cudaSuccess) return e;
     kern<<<static_cast<unsigned>(bh) * pl.nchunks, kStThreads, kStSmem, stream>>>(mq, mk, mv, sp);
     count_launch();
@@ -606,7 +606,7 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, OutParams);
     if (s.out_f32) kern = s.bf16 ? sima_out_kernel<true, true> : sima_out_kernel<false, true>;
     else kern = s.bf16 ? sima_out_kernel<true, false> : sima_out_kernel<false, false>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kOutSmem);
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kOutSmem);
     if (e != cudaSuccess) return e;
     kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads, kOutSmem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);
     count_launch();

@@ -13,7 +13,7 @@ from . import _lib
 from ._lib import AsukaError  # noqa: F401  (re-exported)
 
 _DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32,
-           torch.int32: _lib.I32}
+           torch.int32: _lib.I32, torch.uint8: _lib.U8, torch.bool: _lib.U8}
 
 
 def _desc(t):
@@ -58,8 +58,9 @@ def _same_device(*ts):
       raise RuntimeError("all tensors must be on the same device")
 
 
-def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None):
-  """out = softmax(q k^T * scale (+ causal mask)) v.  q: [B,Sq,H,128]; k, v: [B,Skv,H,128]."""
+def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None, softcap=0.0):
+  """out = softmax(q k^T * scale (+ causal mask)) v.  q: [B,Sq,H,128]; k, v: [B,Skv,H,128].
+  softcap > 0 applies cap * tanh(logits / cap) before the mask (cases/kernels/gemma2.py:30-33)."""
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
   _same_device(q4, k4, v4)
@@ -69,26 +70,28 @@ def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None
     lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32,
                       device=q4.device) if return_lse else None
     p = _lib.AttnParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(lse),
-                        float(softmax_scale), int(bool(causal)))
+                        float(softmax_scale), int(bool(causal)), float(softcap))
     _lib.check("asuka_b200_attn_fwd", lib.asuka_b200_attn_fwd(ctypes.byref(p), _stream(q4)))
   out = out.view(q.shape) if q.dim() == 2 else out
   return (out, lse) if return_lse else out
 
 
 def col_scores(q, k, lse, mode=_lib.SCORE_SUM, causal=True, softmax_scale=0.0, exp_rand=None,
-               tau=1.0, seed=0):
-  """Per-key sums over the query rows of the attention probabilities: [B,H,Skv] f32
-  (and the sum of squares in mode SCORE_SUM_SQ)."""
+               tau=1.0, seed=0, corm_mask=None):
+  """Per-key reductions over the query rows of the attention probabilities: [B,H,Skv] f32 sums
+  (and sums of squares in mode SCORE_SUM_SQ); in mode SCORE_CORM a bool tensor that is True where
+  some probability reaches its threshold in `corm_mask` [Sq, Skv]."""
   lib = _lib.load()
   q4, k4 = _as4d(q), _as4d(k)
-  _same_device(q4, k4, lse, exp_rand)
+  _same_device(q4, k4, lse, exp_rand, corm_mask)
   B, Skv, H = k4.shape[0], k4.shape[1], k4.shape[2]
   with torch.cuda.device(q4.device):
-    score = torch.empty((B, H, Skv), dtype=torch.float32, device=q4.device)
+    score = torch.empty((B, H, Skv), dtype=torch.bool if mode == _lib.SCORE_CORM else torch.float32,
+                        device=q4.device)
     score_sq = torch.empty_like(score) if mode == _lib.SCORE_SUM_SQ else None
     p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _desc(score), _desc(score_sq),
                          _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
-                         int(bool(causal)), int(mode))
+                         int(bool(causal)), int(mode), _desc(corm_mask))
     _lib.check("asuka_b200_col_scores", lib.asuka_b200_col_scores(ctypes.byref(p), _stream(q4)))
   return (score, score_sq) if score_sq is not None else score
 
@@ -102,7 +105,7 @@ def keyformer_rowstat(q, k, causal=True, softmax_scale=0.0, exp_rand=None, tau=1
     lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32, device=q4.device)
     p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _lib.Tensor(), _lib.Tensor(),
                          _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
-                         int(bool(causal)), _lib.SCORE_PERTURBED)
+                         int(bool(causal)), _lib.SCORE_PERTURBED, _lib.Tensor())
     _lib.check("asuka_b200_keyformer_rowstat",
                lib.asuka_b200_keyformer_rowstat(ctypes.byref(p), _stream(q4)))
   return lse
@@ -120,6 +123,18 @@ def select_topk(score, k_keep, mode=_lib.SELECT_TOPK, recent=0, score_sq=None, q
                           int(q_len), int(mode))
     _lib.check("asuka_b200_select_topk", lib.asuka_b200_select_topk(ctypes.byref(p), _stream(score)))
   return idx
+
+
+def pool_scores(score, kernel_size):
+  """SnapKV smoothing: avg_pool1d(score, kernel_size, padding=kernel_size // 2, stride=1) over keys."""
+  lib = _lib.load()
+  _same_device(score)
+  with torch.cuda.device(score.device):
+    out = torch.empty_like(score)
+    a, b = _desc(score), _desc(out)
+    _lib.check("asuka_b200_pool_scores",
+               lib.asuka_b200_pool_scores(ctypes.byref(a), ctypes.byref(b), int(kernel_size), _stream(score)))
+  return out
 
 
 def sima_fwd(q, k, v, out_dtype=None):

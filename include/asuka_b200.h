@@ -50,7 +50,7 @@ typedef enum {
   ASUKA_ERR_TOO_LARGE = -11
 } asuka_status;
 
-typedef enum { ASUKA_F16 = 0, ASUKA_BF16 = 1, ASUKA_F32 = 2, ASUKA_I32 = 3 } asuka_dtype;
+typedef enum { ASUKA_F16 = 0, ASUKA_BF16 = 1, ASUKA_F32 = 2, ASUKA_I32 = 3, ASUKA_U8 = 4 } asuka_dtype;
 
 typedef struct {
   void* ptr;
@@ -76,6 +76,8 @@ typedef struct {
   float softmax_scale; /* <= 0 selects 1/sqrt(128) */
   int32_t causal;      /* 1: key j is visible to query i iff j <= i + (Skv - Sq)
                           (torch.triu(-inf, diagonal=kv_len-q_len+1), cases/kernels/attn.py:22-23) */
+  float softcap;       /* > 0: logits -> softcap * tanh(logits / softcap) before the mask, the
+                          Gemma-2 variant (cases/kernels/gemma2.py:30-33); 0: off */
 } asuka_attn_params;
 
 int asuka_b200_attn_fwd(const asuka_attn_params* p, asuka_stream stream);
@@ -86,7 +88,8 @@ int asuka_b200_attn_fwd(const asuka_attn_params* p, asuka_stream stream);
 typedef enum {
   ASUKA_SCORE_SUM = 0,       /* sum_i p_ij                          (H2O)      */
   ASUKA_SCORE_SUM_SQ = 1,    /* sum_i p_ij and sum_i p_ij^2         (RoCo)     */
-  ASUKA_SCORE_PERTURBED = 2  /* sum_i softmax_j((s_ij + g_ij)/tau)  (Keyformer) */
+  ASUKA_SCORE_PERTURBED = 2, /* sum_i softmax_j((s_ij + g_ij)/tau)  (Keyformer) */
+  ASUKA_SCORE_CORM = 3       /* any_i(p_ij >= mask_ij) -> 0/1 bytes  (CORM, cases/kernels/corm.py:34-37) */
 } asuka_score_mode;
 
 typedef struct {
@@ -94,7 +97,7 @@ typedef struct {
   asuka_tensor k;        /* [B, Skv, H, 128] */
   asuka_tensor lse;      /* [B, H, Sq] f32: row statistic from asuka_b200_attn_fwd (modes 0, 1) or
                             from asuka_b200_keyformer_rowstat (mode 2) */
-  asuka_tensor score;    /* [B, H, Skv] f32 out */
+  asuka_tensor score;    /* [B, H, Skv] f32 out (mode ASUKA_SCORE_CORM: u8, 1 where the key is kept) */
   asuka_tensor score_sq; /* [B, H, Skv] f32 out, mode ASUKA_SCORE_SUM_SQ only */
   asuka_tensor exp_rand; /* mode 2: [B, H, Sq, Skv] f32 > 0, noise g = -log(exp_rand)
                             (cases/kernels/kf.py:36-37); ptr NULL selects the seeded generator */
@@ -103,6 +106,8 @@ typedef struct {
   uint64_t seed;         /* mode 2 with exp_rand.ptr == NULL */
   int32_t causal;
   int32_t mode;          /* asuka_score_mode */
+  asuka_tensor corm_mask; /* mode ASUKA_SCORE_CORM: [Sq, Skv] f32 thresholds (1/(i+1) in the reference's
+                             prepare, cases/kernels/corm.py:46-48), shared by every batch and head */
 } asuka_score_params;
 
 int asuka_b200_col_scores(const asuka_score_params* p, asuka_stream stream);
@@ -131,6 +136,12 @@ typedef struct {
 } asuka_select_params;
 
 int asuka_b200_select_topk(const asuka_select_params* p, asuka_stream stream);
+
+/* ---- SnapKV's score smoothing: out = avg_pool1d(score, kernel_size, padding = kernel_size / 2,
+ *      stride 1) along the key axis (cases/kernels/snapkv.py:35-38).  `score` and `out` are
+ *      [B, H, S] f32, contiguous, and must not overlap; kernel_size is odd. ---- */
+int asuka_b200_pool_scores(const asuka_tensor* score, const asuka_tensor* out, int32_t kernel_size,
+                           asuka_stream stream);
 
 /* ---- SimA softmax-free attention: replaces the generated kernels for bench/sima.mlir:13-17
  *      (L1 normalisation as lib/Dialect/Asuka/Transforms/LowerComplexReduce.cpp:44-69). ---- */

@@ -26,12 +26,18 @@ def load_golden(name):
   if "exp_rand" in z.files:
     d["exp_rand"] = torch.from_numpy(z["exp_rand"].copy())
     d["tau"] = float(z["tau"])
+  for key in ("corm_mask",):
+    if key in z.files:
+      d[key] = torch.from_numpy(z[key].copy())
+  for key in ("softcap", "kernel_size"):
+    if key in z.files:
+      d[key] = z[key].item()
   d["outs"] = [torch.from_numpy(z[f"out{i}"].copy()) for i in range(4) if f"out{i}" in z.files]
   return d
 
 
 GOLDEN_NAMES = ["attn_f16_s256", "attn_f16_q128_kv320", "h2o_f16_b2_s192", "kf_f16_s256",
-                "roco_bf16_s256"]
+                "roco_bf16_s256", "gemma2_f16_s256", "snapkv_f16_s256", "corm_f16_s256"]
 
 
 @pytest.fixture(scope="session")

@@ -4,7 +4,8 @@ Run once where the reference checkout is mounted:
 
     python tests/golden/make_golden.py /root/reference
 
-It imports the reference's own eager modules (cases/kernels/{attn,h2o,kf,roco}.py), unmodified,
+It imports the reference's own eager modules (cases/kernels/{attn,h2o,kf,roco,gemma2,snapkv,corm}.py),
+unmodified,
 runs their ``forward`` on the CPU in fp32 on seeded inputs that were first rounded to fp16/bf16,
 and stores inputs (16-bit) and outputs (fp32) as compressed .npz files.  The tests compare the CPU
 oracle (oracle/attn_oracle.py) and the CUDA kernels against these files; neither the tests nor the
@@ -30,6 +31,9 @@ CASES = [
     ("h2o_f16_b2_s192", "h2o", "H2O", 2, 192, 192, 2, torch.float16, 13),
     ("kf_f16_s256", "kf", "KeyFormer", 1, 256, 256, 2, torch.float16, 14),
     ("roco_bf16_s256", "roco", "RoCo", 1, 256, 256, 2, torch.bfloat16, 15),
+    ("gemma2_f16_s256", "gemma2", "Gemma2", 1, 256, 256, 2, torch.float16, 16),
+    ("snapkv_f16_s256", "snapkv", "SnapKV", 1, 256, 256, 2, torch.float16, 17),
+    ("corm_f16_s256", "corm", "Corm", 1, 256, 256, 2, torch.float16, 18),
 ]
 
 
@@ -42,7 +46,8 @@ def main(ref_root):
   real = torch.cuda.current_device
   torch.cuda.current_device = lambda: "cpu"
   try:
-    mods = {m: importlib.import_module(f"kernels.{m}") for m in ("attn", "h2o", "kf", "roco")}
+    mods = {m: importlib.import_module(f"kernels.{m}")
+            for m in ("attn", "h2o", "kf", "roco", "gemma2", "snapkv", "corm")}
   finally:
     torch.cuda.current_device = real
   for name, mod, cls, B, Sq, Skv, H, dtype, seed in CASES:
@@ -59,11 +64,25 @@ def main(ref_root):
       args.append(er)
       save["exp_rand"] = er.numpy()
       save["tau"] = np.float32(model.tau)
+    if cls == "Corm":
+      cm = torch.ones(Sq, Skv)
+      for i in range(Sq):                 # as the reference's prepare, cases/kernels/corm.py:46-48
+        cm[i] /= i + 1
+      args.append(cm)
+      save["corm_mask"] = cm.numpy()
+    if cls == "Gemma2":
+      # N(0,1) inputs never reach the cap of 50; scale q so that the tanh actually bends the logits
+      q = (q.float() * 12).to(dtype)
+      args[0] = q.float()
+      save["q"] = bits16(q)
+      save["softcap"] = np.float32(model.logit_softcapping)
+    if cls == "SnapKV":
+      save["kernel_size"] = np.int32(model.kernel_size)
     with torch.no_grad():
       outs = model.forward(*args)
     outs = outs if isinstance(outs, tuple) else (outs,)
     for i, o in enumerate(outs):
-      save[f"out{i}"] = o.float().numpy()
+      save[f"out{i}"] = o.numpy() if o.dtype == torch.bool else o.float().numpy()
     path = os.path.join(HERE, name + ".npz")
     np.savez_compressed(path, **save)
     print(name, [tuple(o.shape) for o in outs], os.path.getsize(path) // 1024, "KiB")

@@ -45,7 +45,7 @@ def _t(shape, dtype=_lib.F16, ptr=0x1000, strides=None):
 def _attn(q=None, k=None, v=None, out=None, lse=None, scale=0.0, causal=1):
   shp = (1, 256, 2, 128)
   return _lib.AttnParams(q or _t(shp), k or _t(shp), v or _t(shp), out or _t(shp),
-                         lse or _lib.Tensor(), scale, causal)
+                         lse or _lib.Tensor(), scale, causal, 0.0)
 
 
 def test_attn_validation_codes(built_lib):
@@ -142,7 +142,7 @@ def test_flop_conventions():
 def test_builder_interface():
   assert issubclass(B200Builder, Builder)
   with pytest.raises(ValueError):
-    B200Builder("Gemma2")
+    B200Builder("EA")
   f = B200Builder("H2O").build_callable()
   with pytest.raises(RuntimeError):
     f(torch.zeros(1), torch.zeros(1))                     # wrong arity

@@ -18,6 +18,12 @@ def _run_oracle(name, g):
     return O.keyformer(q, k, v, g["exp_rand"], g["tau"])
   if name.startswith("roco"):
     return O.roco(q, k, v)
+  if name.startswith("gemma2"):
+    return (O.gemma2(q, k, v, g["softcap"]),)
+  if name.startswith("snapkv"):
+    return O.snapkv(q, k, v, g["kernel_size"])
+  if name.startswith("corm"):
+    return O.corm(q, k, v, g["corm_mask"])[:2]
   raise AssertionError(name)
 
 
@@ -28,6 +34,9 @@ def test_oracle_matches_reference_fixture(name):
   assert len(outs) == len(g["outs"])
   for got, want in zip(outs, g["outs"]):
     assert got.shape == want.shape
+    if want.dtype == torch.bool:
+      assert torch.equal(got, want)
+      continue
     # same torch ops in the same order on the same host: differences are rounding noise only
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
 

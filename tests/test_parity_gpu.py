@@ -44,20 +44,36 @@ def no_timeouts(ops):
 # ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("name", GOLDEN_NAMES)
 def test_against_reference_fixture(ops, name):
+  import flashtensor_b200 as ft
   g = load_golden(name)
   q, k, v = g["q"].cuda(), g["k"].cuda(), g["v"].cuda()
+  H = q.shape[2]
   if name.startswith("attn"):
     outs = (ops.attn_fwd(q, k, v),)
   elif name.startswith("h2o"):
     outs = ops.h2o(q, k, v)
   elif name.startswith("kf"):
     outs = ops.keyformer(q, k, v, g["exp_rand"].cuda(), tau=g["tau"])
-  else:
+  elif name.startswith("roco"):
     outs = ops.roco(q, k, v)
+  elif name.startswith("gemma2"):
+    outs = (ft.Gemma2(logit_softcapping=g["softcap"], head_num=H, kv_head_num=H).forward(q, k, v),)
+  elif name.startswith("snapkv"):
+    outs = ft.SnapKV(kernel_size=g["kernel_size"], head_num=H, kv_head_num=H).forward(q, k, v)
+  else:
+    outs = ft.Corm(head_num=H, kv_head_num=H).forward(q, k, v, g["corm_mask"].cuda())
   torch.cuda.synchronize()
   assert len(outs) == len(g["outs"])
   for i, (got, want) in enumerate(zip(outs, g["outs"])):
     assert tuple(got.shape) == tuple(want.shape)
+    if want.dtype == torch.bool:
+      # a keep decision may differ from the reference's only where it hangs on rounding: some
+      # probability within 1e-3 (relative) of its threshold
+      _, _, margin = O.corm(g["q"], g["k"], g["v"], g["corm_mask"])
+      differ = got.cpu() != want
+      assert got.dtype == torch.bool and want.any() and not want.all()
+      assert torch.all((margin[differ] - 1).abs() < 1e-3), f"{int(differ.sum())} decisions differ off the threshold"
+      continue
     close(got, want, f"{name} output {i}")
   no_timeouts(ops)
 
@@ -182,6 +198,32 @@ def test_logits_that_keep_growing_or_shrinking(ops, dtype, direction):
     torch.cuda.synchronize()
     close(out, ref_out, "out")
     close(score, ref_score, "score")
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_sibling_cases_vs_oracle(ops, dtype):
+  # Gemma-2 soft-capping, SnapKV pooling and CORM thresholds on ragged and rectangular shapes
+  import flashtensor_b200 as ft
+  for (B, Sq, Skv, H) in [(2, 200, 200, 3), (1, 130, 390, 2), (1, 1024, 1024, 2)]:
+    q, k, v = O.make_inputs("attn", B, Sq, Skv, H, 128, dtype, seed=Sq)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    for cap, qs in ((50.0, 1.0), (30.0, 16.0)):      # the second one drives logits deep into the cap
+      qq = (q.float() * qs).to(dtype)
+      out = ft.Gemma2(logit_softcapping=cap, head_num=H, kv_head_num=H)(qq.cuda(), kd, vd)
+      close(out, O.gemma2(qq, k, v, cap), f"gemma2 cap {cap}")
+    for ks in (1, 5, 9):
+      out, score = ft.SnapKV(kernel_size=ks, head_num=H, kv_head_num=H)(qd, kd, vd)
+      ref_out, ref_score = O.snapkv(q, k, v, ks)
+      close(out, ref_out, "snapkv out")
+      close(score, ref_score, f"snapkv score k={ks}")
+    mask = O.corm_mask(Sq, Skv)
+    out, keep = ft.Corm(head_num=H, kv_head_num=H)(qd, kd, vd, mask.cuda())
+    ref_out, ref_keep, margin = O.corm(q, k, v, mask)
+    close(out, ref_out, "corm out")
+    differ = keep.cpu() != ref_keep
+    assert torch.all((margin[differ] - 1).abs() < 1e-3)
+    assert differ.float().mean() < 0.01
   no_timeouts(ops)
 
 
