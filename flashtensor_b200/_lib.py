@@ -48,6 +48,10 @@ class SimaParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor)]
 
 
+class GatherParams(ctypes.Structure):
+  _fields_ = [("k", Tensor), ("v", Tensor), ("idx", Tensor), ("k_out", Tensor), ("v_out", Tensor)]
+
+
 class CaseParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor), ("score", Tensor),
               ("score_sq", Tensor), ("exp_rand", Tensor), ("idx", Tensor),
@@ -72,6 +76,7 @@ SYMBOLS = {
     "asuka_b200_keyformer_rowstat": (ctypes.c_int, [ctypes.POINTER(ScoreParams), ctypes.c_void_p]),
     "asuka_b200_select_topk": (ctypes.c_int, [ctypes.POINTER(SelectParams), ctypes.c_void_p]),
     "asuka_b200_pool_scores": (ctypes.c_int, [ctypes.POINTER(Tensor), ctypes.POINTER(Tensor), ctypes.c_int32, ctypes.c_void_p]),
+    "asuka_b200_gather_kv": (ctypes.c_int, [ctypes.POINTER(GatherParams), ctypes.c_void_p]),
     "asuka_b200_sima_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_sima_fwd": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_case_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.POINTER(ctypes.c_size_t)]),

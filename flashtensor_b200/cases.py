@@ -17,6 +17,7 @@ from . import ops
 
 class _Case:
   output_names = ["out"]
+  allow_gqa = False
 
   def __init__(self, kv_head_num=32, head_num=32, head_dim=128):
     if head_dim != 128:
@@ -27,8 +28,11 @@ class _Case:
     self.hidden_size = head_num * head_dim
     self.kv_hidden_size = kv_head_num * head_dim
     self.group_size = self.head_num // self.kv_head_num
-    # same restriction as the reference's 4-D cases (cases/kernels/h2o.py:16)
-    assert self.group_size == 1
+    # the reference's 4-D cases assert group_size == 1 (cases/kernels/h2o.py:16); its 2-D case
+    # scripts (cases/attn.py, cases/attn_h2o.py) run grouped-query attention, supported here by
+    # the classes that set `allow_gqa`
+    assert self.head_num % self.kv_head_num == 0
+    assert self.group_size == 1 or self.allow_gqa, "grouped-query attention: Attn, Gemma2, H2O only"
 
   def __call__(self, *args, **kwargs):
     return self.forward(*args, **kwargs)
@@ -48,7 +52,7 @@ class _Case:
     """Random inputs of the case's shapes, as ``prepare`` in cases/kernels/h2o.py:41-58."""
     device = torch.cuda.current_device() if device is None else device
     shape_q = (batch_size, q_len, self.head_num, self.head_dim)
-    shape_kv = (batch_size, kv_len, self.head_num, self.head_dim)
+    shape_kv = (batch_size, kv_len, self.kv_head_num, self.head_dim)
     q = torch.randn(shape_q, dtype=dtype, device=device)
     k = torch.randn(shape_kv, dtype=dtype, device=device)
     v = torch.randn(shape_kv, dtype=dtype, device=device)
@@ -56,8 +60,10 @@ class _Case:
 
 
 class Attn(_Case):
-  """cases/kernels/attn.py:7-34.  ``causal=False`` gives ``forward_wo_mask`` of cases/attn.py."""
+  """cases/kernels/attn.py:7-34.  ``causal=False`` gives ``forward_wo_mask`` of cases/attn.py;
+  kv_head_num < head_num is the grouped-query form of cases/attn.py:20-42."""
   output_names = ["out"]
+  allow_gqa = True
 
   def __init__(self, kv_head_num=32, head_num=32, head_dim=128, causal=True):
     super().__init__(kv_head_num, head_num, head_dim)
@@ -71,6 +77,7 @@ class Attn(_Case):
 class Gemma2(_Case):
   """cases/kernels/gemma2.py: attention with soft-capped logits, cap * tanh(logits / cap)."""
   output_names = ["out"]
+  allow_gqa = True
 
   def __init__(self, logit_softcapping=50.0, kv_head_num=32, head_num=32, head_dim=128, causal=True):
     super().__init__(kv_head_num, head_num, head_dim)
@@ -83,8 +90,10 @@ class Gemma2(_Case):
 
 
 class H2O(_Case):
-  """cases/kernels/h2o.py:7-38: returns (out, h2o_score [B,H,Skv] f32)."""
+  """cases/kernels/h2o.py:7-38: returns (out, h2o_score [B,Hkv,Skv] f32).  With kv_head_num <
+  head_num the score is the mean over each group of query heads (cases/attn_h2o.py:42-46)."""
   output_names = ["out", "h2o_score"]
+  allow_gqa = True
 
   def __init__(self, kv_head_num=32, head_num=32, head_dim=128, causal=True):
     super().__init__(kv_head_num, head_num, head_dim)

@@ -47,6 +47,7 @@ struct FwdParams {
   int B, H, Sq, Skv;
   int causal, diag_off;
   int nq_blocks, n_items;
+  int group;                 // query heads per key/value head (grouped-query attention)
   float scale_log2;          // softmax_scale * log2(e)
   float cap_in, cap_out;     // soft-capping: softmax_scale / cap and cap * log2(e)
   float* lse2;
@@ -232,8 +233,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           const uint32_t bar = smem_u32(&bars.k_full[st]);
           mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, it_.h, j * kTile, it_.b);
-          tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, it_.h, j * kTile, it_.b);
+          tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, it_.h / p.group, j * kTile, it_.b);
+          tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, it_.h / p.group, j * kTile, it_.b);
         }
       }
       if (!ok) {
@@ -261,8 +262,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           const uint32_t bar = smem_u32(&bars.v_full[st]);
           mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, it_.h, j * kTile, it_.b);
-          tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, it_.h, j * kTile, it_.b);
+          tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, it_.h / p.group, j * kTile, it_.b);
+          tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, it_.h / p.group, j * kTile, it_.b);
         }
       }
       if (!ok) {
@@ -575,6 +576,7 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.diag_off = s.Skv - s.Sq;
   p.nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
   p.n_items = p.nq_blocks * s.B * s.H;
+  p.group = s.group;
   p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
   p.cap_in = s.softcap > 0.f ? s.softmax_scale / s.softcap : 0.f;
   p.cap_out = s.softcap * 1.4426950408889634f;

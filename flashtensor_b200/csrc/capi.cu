@@ -128,13 +128,16 @@ int check_qk(const asuka_tensor& q, const asuka_tensor& k, float scale, int caus
   int r;
   if ((r = check_bshd(q, q.dtype)) != ASUKA_OK) return r;
   if ((r = check_bshd(k, q.dtype)) != ASUKA_OK) return r;
-  if (k.shape[0] != q.shape[0] || k.shape[2] != q.shape[2]) return ASUKA_ERR_BAD_SHAPE;
+  // grouped-query attention: the query heads are a whole multiple of the key/value heads
+  if (k.shape[0] != q.shape[0] || k.shape[2] > q.shape[2] || q.shape[2] % k.shape[2] != 0)
+    return ASUKA_ERR_BAD_SHAPE;
   if (causal && k.shape[1] < q.shape[1]) return ASUKA_ERR_BAD_SHAPE;
   if (std::isnan(scale) || std::isinf(scale)) return ASUKA_ERR_BAD_ARGUMENT;
   o->dtype = q.dtype;
   o->s.B = static_cast<int>(q.shape[0]);
   o->s.Sq = static_cast<int>(q.shape[1]);
   o->s.H = static_cast<int>(q.shape[2]);
+  o->s.group = static_cast<int>(q.shape[2] / k.shape[2]);
   o->s.Skv = static_cast<int>(k.shape[1]);
   o->s.causal = causal ? 1 : 0;
   o->s.softmax_scale = scale > 0.f ? scale : 1.0f / std::sqrt(static_cast<float>(kHeadDim));
@@ -354,9 +357,18 @@ int sima_impl(const asuka_sima_params* p, void* ws, size_t ws_bytes, cudaStream_
 // forward + column scores (+ selection) on one stream; the row statistic lives in `ws`
 enum CaseKind { CASE_H2O, CASE_ROCO, CASE_KF };
 
-size_t case_ws_bytes(const asuka_case_params* p) {
+size_t case_rowstat_bytes(const asuka_case_params* p) {
   const size_t n = static_cast<size_t>(p->q.shape[0]) * p->q.shape[2] * p->q.shape[1];
   return ((n * sizeof(float) + 255) / 256) * 256 * 2;  // unperturbed + perturbed row statistics
+}
+// grouped-query attention also parks the per-query-head scores [B, H, Skv] before the group mean
+size_t case_ws_bytes(const asuka_case_params* p) {
+  size_t bytes = case_rowstat_bytes(p);
+  if (p->k.ndim == 4 && p->k.shape[2] > 0 && p->q.shape[2] > p->k.shape[2]) {
+    const size_t n = static_cast<size_t>(p->q.shape[0]) * p->q.shape[2] * p->k.shape[1];
+    bytes += ((n * sizeof(float) + 255) / 256) * 256;
+  }
+  return bytes;
 }
 
 int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_bytes,
@@ -370,7 +382,8 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
   if (ws_bytes < case_ws_bytes(p)) return ASUKA_ERR_WORKSPACE_TOO_SMALL;
   const int64_t B = p->q.shape[0], Sq = p->q.shape[1], H = p->q.shape[2];
   float* lse = static_cast<float*>(ws);
-  float* lse_kf = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + case_ws_bytes(p) / 2);
+  float* lse_kf = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + case_rowstat_bytes(p) / 2);
+  float* head_scores = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + case_rowstat_bytes(p));
 
   // validate everything before the first launch
   asuka_tensor lse_t;
@@ -410,6 +423,26 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
     lp.mode = kind == CASE_H2O ? ASUKA_SELECT_TOPK_RECENT : kind == CASE_ROCO ? ASUKA_SELECT_ROCO : ASUKA_SELECT_TOPK;
   }
 
+  // grouped-query attention (H2O only; cases/attn_h2o.py:42-46): the column kernel writes one
+  // score row per QUERY head into the workspace, the group mean lands in p->score [B, Hkv, Skv]
+  const int64_t Hkv = p->k.ndim == 4 ? p->k.shape[2] : 0;
+  const bool gqa = Hkv > 0 && H > Hkv;
+  asuka_tensor head_score_t;
+  std::memset(&head_score_t, 0, sizeof(head_score_t));
+  if (gqa) {
+    if (kind != CASE_H2O) return ASUKA_ERR_BAD_SHAPE;
+    const int64_t Skv = p->k.shape[1];
+    head_score_t.ptr = head_scores;
+    head_score_t.dtype = ASUKA_F32;
+    head_score_t.ndim = 3;
+    head_score_t.shape[0] = B; head_score_t.shape[1] = H; head_score_t.shape[2] = Skv;
+    head_score_t.stride[0] = H * Skv; head_score_t.stride[1] = Skv; head_score_t.stride[2] = 1;
+    const int64_t gshape[3] = {B, Hkv, Skv};
+    int r0 = check_dense(p->score, ASUKA_F32, 3, gshape);
+    if (r0 != ASUKA_OK) return r0;
+    sp.score = head_score_t;
+  }
+
   // dry validation pass: the three impls validate before launching, so run their checks first
   {
     QKV c; ScoreArgs a;
@@ -425,7 +458,7 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
       const int recent = kind == CASE_H2O ? p->recent : 0;
       if (S > (roco ? kSelectMaxS64 : kSelectMaxS32)) return ASUKA_ERR_TOO_LARGE;
       if (recent < 0 || recent > S || p->k_keep < 1 || p->k_keep > S - recent) return ASUKA_ERR_BAD_ARGUMENT;
-      const int64_t ishape[3] = {B, H, p->k_keep + recent};
+      const int64_t ishape[3] = {B, gqa ? Hkv : H, p->k_keep + recent};
       if ((r = check_dense(p->idx, ASUKA_I32, 3, ishape)) != ASUKA_OK) return r;
     }
   }
@@ -436,6 +469,11 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
     if ((r = kf_rowstat_impl(&sp, stream)) != ASUKA_OK) return r;
   }
   if ((r = col_scores_impl(&sp, stream)) != ASUKA_OK) return r;
+  if (gqa) {
+    r = map_cuda(launch_group_mean(head_scores, static_cast<float*>(p->score.ptr), static_cast<int>(B * Hkv),
+                                   static_cast<int>(H / Hkv), static_cast<int>(p->k.shape[1]), stream));
+    if (r != ASUKA_OK) return r;
+  }
   if (want_idx) r = select_impl(&lp, stream);
   return r;
 }
@@ -542,6 +580,39 @@ int asuka_b200_pool_scores(const asuka_tensor* score, const asuka_tensor* out, i
   return map_cuda(launch_pool_scores(static_cast<const float*>(score->ptr), static_cast<float*>(out->ptr),
                                      static_cast<int>(shp[0] * shp[1]), static_cast<int>(shp[2]),
                                      kernel_size, static_cast<cudaStream_t>(stream)));
+}
+
+int asuka_b200_gather_kv(const asuka_gather_params* p, asuka_stream stream) {
+  if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (!is_16bit(p->k.dtype)) return p->k.ptr == nullptr ? ASUKA_ERR_NULL_POINTER : ASUKA_ERR_BAD_DTYPE;
+  int r;
+  if ((r = check_bshd(p->k, p->k.dtype)) != ASUKA_OK) return r;
+  if ((r = check_bshd(p->v, p->k.dtype)) != ASUKA_OK) return r;
+  if ((r = check_bshd(p->k_out, p->k.dtype)) != ASUKA_OK) return r;
+  if ((r = check_bshd(p->v_out, p->k.dtype)) != ASUKA_OK) return r;
+  const int64_t B = p->k.shape[0], S = p->k.shape[1], H = p->k.shape[2];
+  if (p->idx.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
+  if (p->idx.ndim != 3 || p->idx.shape[0] != B || p->idx.shape[1] != H || p->idx.shape[2] <= 0)
+    return ASUKA_ERR_BAD_SHAPE;
+  const int64_t n = p->idx.shape[2];
+  const int64_t ishape[3] = {B, H, n};
+  if ((r = check_dense(p->idx, ASUKA_I32, 3, ishape)) != ASUKA_OK) return r;
+  for (int i = 0; i < 4; ++i) {
+    if (p->v.shape[i] != p->k.shape[i] || p->v.stride[i] != p->k.stride[i]) return ASUKA_ERR_BAD_SHAPE;
+    if (p->v_out.shape[i] != p->k_out.shape[i] || p->v_out.stride[i] != p->k_out.stride[i]) return ASUKA_ERR_BAD_SHAPE;
+  }
+  if (p->k_out.shape[0] != B || p->k_out.shape[1] != n || p->k_out.shape[2] != H) return ASUKA_ERR_BAD_SHAPE;
+  if ((r = check_arch()) != ASUKA_OK) return r;
+  GatherArgs a;
+  a.k = static_cast<const uint16_t*>(p->k.ptr);
+  a.v = static_cast<const uint16_t*>(p->v.ptr);
+  a.k_out = static_cast<uint16_t*>(p->k_out.ptr);
+  a.v_out = static_cast<uint16_t*>(p->v_out.ptr);
+  a.idx = static_cast<const int32_t*>(p->idx.ptr);
+  a.B = static_cast<int>(B); a.H = static_cast<int>(H); a.S = static_cast<int>(S); a.n = static_cast<int>(n);
+  a.in_sb = p->k.stride[0]; a.in_ss = p->k.stride[1]; a.in_sh = p->k.stride[2];
+  a.out_sb = p->k_out.stride[0]; a.out_ss = p->k_out.stride[1]; a.out_sh = p->k_out.stride[2];
+  return map_cuda(launch_gather_kv(a, static_cast<cudaStream_t>(stream)));
 }
 
 int asuka_b200_sima_workspace_bytes(const asuka_sima_params* p, size_t* bytes) {

@@ -43,6 +43,7 @@ struct ColParams {
   int B, H, Sq, Skv;
   int causal, diag_off;
   int nq_tiles;
+  int group;          // query heads per key head (grouped-query attention)
   float scale_log2;   // softmax_scale * log2(e) (perturbed mode: additionally / tau)
   float inv_tau;
   const float* lse2;  // [B,H,Sq]
@@ -170,8 +171,8 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       mbar_expect_tx(bar, kTileBytes * n_active);
       for (int t = 0; t < 2; ++t) {
         if (active[t]) {
-          tma_load_4d(sK + t * kTileBytes, &map_k, bar, 0, h, kv0[t], b);
-          tma_load_4d(sK + t * kTileBytes + kHalfBytes, &map_k, bar, 64, h, kv0[t], b);
+          tma_load_4d(sK + t * kTileBytes, &map_k, bar, 0, h / p.group, kv0[t], b);
+          tma_load_4d(sK + t * kTileBytes + kHalfBytes, &map_k, bar, 64, h / p.group, kv0[t], b);
         }
       }
     }
@@ -467,8 +468,8 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t bar = smem_u32(&bars.k_full[st]);
         const uint32_t base = sStage + st * Cfg::kStageBytes;
         mbar_expect_tx(bar, Cfg::kStageBytes);
-        tma_load_4d(base, &map_k, bar, 0, h, j * kTile, b);
-        tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h, j * kTile, b);
+        tma_load_4d(base, &map_k, bar, 0, h / p.group, j * kTile, b);
+        tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h / p.group, j * kTile, b);
         if constexpr (kNoiseTma) {
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4)
@@ -602,6 +603,7 @@ ColParams make_params(const ScoreArgs& a, const AttnShape& s) {
   p.causal = s.causal;
   p.diag_off = s.Skv - s.Sq;
   p.nq_tiles = (s.Sq + kTile - 1) / kTile;
+  p.group = s.group;
   const float log2e = 1.4426950408889634f;
   p.inv_tau = 1.0f;
   p.scale_log2 = s.softmax_scale * log2e;

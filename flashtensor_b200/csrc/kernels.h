@@ -15,7 +15,8 @@ void count_launch();
 cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 
 struct AttnShape {
-  int B, H, Sq, Skv;
+  int B, H, Sq, Skv;  // H: query heads
+  int group;          // query heads per key/value head (1: multi-head attention)
   int causal;
   float softmax_scale;
   float softcap;  // > 0: logits -> softcap * tanh(logits / softcap) before the mask; 0: off
@@ -52,9 +53,24 @@ struct SelectArgs {
 };
 cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream);
 
+// mean over each group of `group` consecutive heads: [rows * group, S] -> [rows, S]
+cudaError_t launch_group_mean(const float* in, float* out, int rows, int group, int S, cudaStream_t stream);
 // moving average over the key axis of [rows, S] scores (odd kernel size, zero padding)
 cudaError_t launch_pool_scores(const float* in, float* out, int rows, int S, int ksize,
                                cudaStream_t stream);
+
+// KV-cache compaction: rows of k and v (16-bit, [B,S,H,128], strides in elements, same for both)
+// gathered at idx [B,H,n] into [B,n,H,128] outputs
+struct GatherArgs {
+  const uint16_t* k;
+  const uint16_t* v;
+  uint16_t* k_out;
+  uint16_t* v_out;
+  const int32_t* idx;
+  int B, H, S, n;
+  int64_t in_sb, in_ss, in_sh, out_sb, out_ss, out_sh;
+};
+cudaError_t launch_gather_kv(const GatherArgs& a, cudaStream_t stream);
 
 struct SimaShape {
   int B, H, S;

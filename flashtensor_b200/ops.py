@@ -137,6 +137,20 @@ def pool_scores(score, kernel_size):
   return out
 
 
+def gather_kv(k, v, idx):
+  """Compact the KV cache to the kept keys: (k[b, idx[b,h,n], h, :], v alike) as [B, n, H, 128]."""
+  lib = _lib.load()
+  _same_device(k, v, idx)
+  B, _, H, D = k.shape
+  n = idx.shape[2]
+  with torch.cuda.device(k.device):
+    k_out = torch.empty((B, n, H, D), dtype=k.dtype, device=k.device)
+    v_out = torch.empty_like(k_out)
+    p = _lib.GatherParams(_desc(k), _desc(v), _desc(idx), _desc(k_out), _desc(v_out))
+    _lib.check("asuka_b200_gather_kv", lib.asuka_b200_gather_kv(ctypes.byref(p), _stream(k)))
+  return k_out, v_out
+
+
 def sima_fwd(q, k, v, out_dtype=None):
   """SimA: out = L1norm_seq(q) (L1norm_seq(k)^T v), [B,S,H,128]."""
   lib = _lib.load()
@@ -160,6 +174,7 @@ def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None,
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
   _same_device(q4, k4, v4, exp_rand)
+  # scores and indices are per key/value head (with grouped-query attention: the group mean)
   B, Skv, H = k4.shape[0], k4.shape[1], k4.shape[2]
   dev = q4.device
   with torch.cuda.device(dev):

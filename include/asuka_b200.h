@@ -143,6 +143,15 @@ int asuka_b200_select_topk(const asuka_select_params* p, asuka_stream stream);
 int asuka_b200_pool_scores(const asuka_tensor* score, const asuka_tensor* out, int32_t kernel_size,
                            asuka_stream stream);
 
+/* ---- KV-cache compaction, the step after a selection: k_out[b, n, h, :] = k[b, idx[b, h, n], h, :]
+ *      and the same for v.  The reference has no counterpart (it stops at the scores).
+ *      k, v: [B, S, H, 128] 16-bit with identical strides; idx: [B, H, n] i32 with values in [0, S);
+ *      k_out, v_out: [B, n, H, 128], same dtype, identical strides. ---- */
+typedef struct {
+  asuka_tensor k, v, idx, k_out, v_out;
+} asuka_gather_params;
+int asuka_b200_gather_kv(const asuka_gather_params* p, asuka_stream stream);
+
 /* ---- SimA softmax-free attention: replaces the generated kernels for bench/sima.mlir:13-17
  *      (L1 normalisation as lib/Dialect/Asuka/Transforms/LowerComplexReduce.cpp:44-69). ---- */
 typedef struct {

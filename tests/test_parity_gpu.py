@@ -227,6 +227,32 @@ def test_sibling_cases_vs_oracle(ops, dtype):
   no_timeouts(ops)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_grouped_query_attention(ops, dtype):
+  # kv_head_num < head_num (cases/attn.py, cases/attn_h2o.py): shared K/V heads, group-mean score
+  import flashtensor_b200 as ft
+  for (B, Sq, Skv, H, Hkv) in [(1, 256, 256, 8, 2), (2, 200, 333, 6, 3), (1, 1024, 1024, 4, 1)]:
+    g = torch.Generator().manual_seed(Sq + H)
+    q = torch.randn(B, Sq, H, 128, generator=g).to(dtype)
+    k = torch.randn(B, Skv, Hkv, 128, generator=g).to(dtype)
+    v = torch.randn(B, Skv, Hkv, 128, generator=g).to(dtype)
+    ref_out, ref_score = O.h2o_gqa(q, k, v)
+    model = ft.H2O(head_num=H, kv_head_num=Hkv)
+    out, score = model(q.cuda(), k.cuda(), v.cuda())
+    assert score.shape == (B, Hkv, Skv)
+    close(out, ref_out, "gqa out")
+    close(score, ref_score, "gqa score")
+    out_a = ft.Attn(head_num=H, kv_head_num=Hkv)(q.cuda(), k.cuda(), v.cuda())
+    assert torch.equal(out_a, out)
+    k_keep = Skv // 8
+    _, _, idx = model.select(q.cuda(), k.cuda(), v.cuda(), k_keep, 16)
+    assert idx.shape == (B, Hkv, k_keep + 16)
+    assert np.array_equal(idx.cpu().numpy(), O.h2o_select(score.cpu().numpy(), k_keep, 16))
+  with pytest.raises(AssertionError):
+    ft.RoCo(head_num=8, kv_head_num=2)
+  no_timeouts(ops)
+
+
 def test_layouts_strided_and_2d(ops):
   # heads sliced out of a larger buffer (non-contiguous), and the 2-D [S, H*D] layout of cases/attn.py
   B, S, H = 2, 256, 4
@@ -324,6 +350,22 @@ def test_roco_and_keyformer_selection(ops, dtype):
   ref = O.keyformer(q, k, v, er, 1.5)[1].numpy()
   O.check_index_sets(idx, O.keyformer_select(ref, S // 4), ref, S // 4)
   no_timeouts(ops)
+
+
+def test_kv_cache_compaction(ops):
+  # bit-exact gather of the kept rows, on the index sets a selection produces and on strided caches
+  B, S, H, k_keep, recent = 2, 640, 3, 80, 32
+  q, k, v = O.make_inputs("h2o", B, S, S, H, 128, torch.bfloat16, seed=41)
+  kd, vd = k.cuda(), v.cuda()
+  _, _, idx = ops.h2o(q.cuda(), kd, vd, k_keep=k_keep, recent=recent)
+  ko, vo = ops.gather_kv(kd, vd, idx)
+  assert ko.shape == (B, k_keep + recent, H, 128)
+  gi = idx.long().permute(0, 2, 1)[..., None].expand(-1, -1, -1, 128)    # [B, n, H, 128]
+  assert torch.equal(ko, torch.gather(kd, 1, gi)) and torch.equal(vo, torch.gather(vd, 1, gi))
+  big_k = torch.randn(B, S, H + 1, 128, device="cuda").bfloat16()
+  big_v = torch.randn(B, S, H + 1, 128, device="cuda").bfloat16()
+  ko, vo = ops.gather_kv(big_k[:, :, 1:], big_v[:, :, 1:], idx)
+  assert torch.equal(ko, torch.gather(big_k[:, :, 1:], 1, gi)) and torch.equal(vo, torch.gather(big_v[:, :, 1:], 1, gi))
 
 
 # ------------------------------------------------------------------------------------------
