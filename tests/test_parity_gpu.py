@@ -253,6 +253,32 @@ def test_grouped_query_attention(ops, dtype):
   no_timeouts(ops)
 
 
+def test_host_pipeline(ops):
+  # the host-buffer front end delivers the same bits as direct calls, for more calls than slots
+  import flashtensor_b200 as ft
+  from flashtensor_b200.host import HostPipeline
+  model = ft.H2O(head_num=4, kv_head_num=4)
+  fn = lambda q, k, v: model.select(q, k, v, 32, 16)
+  calls = []
+  for s in range(5):
+    g = torch.Generator().manual_seed(100 + s)
+    ins = [torch.randn(1, 384, 4, 128, generator=g).half().pin_memory() for _ in range(3)]
+    want = [t.cpu() for t in fn(*[t.cuda() for t in ins])]
+    outs = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in want]
+    calls.append((ins, outs, want))
+  pipe = HostPipeline(fn, [t.cuda() for t in calls[0][0]], depth=2)
+  pipe.begin()
+  for ins, outs, _ in calls:
+    pipe.submit(ins, outs)
+  pipe.drain()
+  for _, outs, want in calls:
+    for o, w in zip(outs, want):
+      assert torch.equal(o, w)
+  with pytest.raises(ValueError):
+    pipe.submit([t.clone() for t in calls[0][0]], calls[0][1])  # not pinned
+  no_timeouts(ops)
+
+
 def test_layouts_strided_and_2d(ops):
   # heads sliced out of a larger buffer (non-contiguous), and the 2-D [S, H*D] layout of cases/attn.py
   B, S, H = 2, 256, 4
