@@ -592,6 +592,8 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   else kern = s.bf16 ? attn_fwd_kernel<true, false> : attn_fwd_kernel<false, false>;
   cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (e != cudaSuccess) return e;
+  e = check_register_budget(reinterpret_cast<const void*>(kern), kThreads, 128 * kUtilRegs + 256 * kSoftmaxRegs);
+  if (e != cudaSuccess) return e;
   kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
   count_launch();
   return cudaPeekAtLastError();

@@ -44,6 +44,25 @@ cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
   return e;
 }
 
+// setmaxnreg moves registers between the warps of a CTA, but only within what the CTA got at
+// launch (registers per thread x threads); a role asking for more than its share of that pool
+// would wait for ever.  Refuse to launch instead.
+cudaError_t check_register_budget(const void* kernel, int threads, int regs_wanted_total) {
+  struct Entry { const void* k; int total; };
+  static std::mutex mu;
+  static Entry seen[256];
+  static int n_seen = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i].k == kernel) return regs_wanted_total <= seen[i].total ? cudaSuccess : cudaErrorLaunchOutOfResources;
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+  if (e != cudaSuccess) return e;
+  const int total = attr.numRegs * threads;
+  if (n_seen < 256) seen[n_seen++] = Entry{kernel, total};
+  return regs_wanted_total <= total ? cudaSuccess : cudaErrorLaunchOutOfResources;
+}
+
 namespace {
 
 constexpr int kHeadDim = 128;

@@ -12,8 +12,12 @@
 // cross-thread or cross-CTA reduction exists, and results are bitwise reproducible.
 //   warp 0      producer: two resident K tiles (256 keys), Q tiles + their row statistics in a ring
 //   warp 1      tcgen05.mma issuer: S^T_t[buf] = K_t Q_i^T into one of two TMEM buffers per key tile
-//   warps 4-7   keys   0..127 of the block: exp2, mask, accumulate
-//   warps 8-11  keys 128..255
+//   warps 4-11  keys   0..127 of the block: exp2, mask, accumulate; two warps per 32 keys, one for
+//               queries 0..63 and one for queries 64..127 of every query tile
+//   warps 12-19 keys 128..255, likewise
+// Four key warps per scheduler, not two: one warp's stream of FFMA -> MUFU -> FADD chains stalls
+// on its own latencies about half the time, and its loads and barrier waits stall it outright, so
+// two warps leave the MUFU idle a third of the time.
 //
 // The Keyformer row pass (kf_rowstat) is the row-oriented counterpart: S = Q K^T, one thread per
 // query row, online max/sum of the perturbed logits, nothing else.
@@ -34,9 +38,8 @@ constexpr int kTile = 128;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
 constexpr int kQStages = 4;
-constexpr int kThreads = 384;
-constexpr int kColUtilRegs = 96;   // 128 * 96 + 256 * 200 <= 384 * 168
-constexpr int kColKeyRegs = 200;
+constexpr int kThreads = 640;      // 4 utility warps + 16 key warps
+// 640 threads x 96 registers at launch; no role needs more, so no setmaxnreg here
 constexpr uint32_t kSmemBytes = (2 + kQStages) * kTileBytes + 1024;
 
 struct ColParams {
@@ -111,6 +114,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) ColBars bars;
   __shared__ __align__(16) float lse_s[kQStages][kTile];
+  __shared__ float part_s[2][2][2][kTile];  // [sum, sum of squares][query half][key tile][key]
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
 
@@ -141,12 +145,12 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_init(smem_u32(&bars.k_full), 1);
     for (int i = 0; i < kQStages; ++i) {
       mbar_init(smem_u32(&bars.q_full[i]), 1);
-      mbar_init(smem_u32(&bars.q_empty[i]), 1 + 4 * n_active);
+      mbar_init(smem_u32(&bars.q_empty[i]), 1 + 8 * n_active);
     }
     for (int t = 0; t < 2; ++t)
       for (int i = 0; i < 2; ++i) {
         mbar_init(smem_u32(&bars.s_full[t][i]), 1);
-        mbar_init(smem_u32(&bars.s_empty[t][i]), 128);
+        mbar_init(smem_u32(&bars.s_empty[t][i]), 256);
       }
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -162,10 +166,8 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
 
-  // 384 threads x 168 registers: the utility warps hand registers to the per-key warps
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (whole warp)
-    reg_dealloc<kColUtilRegs>();
     if (lane == 0) {
       const uint32_t bar = smem_u32(&bars.k_full);
       mbar_expect_tx(bar, kTileBytes * n_active);
@@ -208,7 +210,6 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     // The whole warp walks the loop (warp-uniform descriptors, converged waits); one elected lane
     // issues the tcgen05.mma / commit instructions.
-    reg_dealloc<kColUtilRegs>();
     {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
@@ -253,12 +254,12 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
     }
   } else if (warp < 4) {
-    reg_dealloc<kColUtilRegs>();
   } else {
-    // ------------------------------------------------------------------ one thread per key
-    reg_alloc<kColKeyRegs>();
-    const int t = (warp - 4) >> 2;
-    const int wq = warp & 3;
+    // ------------------------------------------------------------------ one thread per (key, query half)
+    const int kw = warp - 4;
+    const int t = kw >> 3;         // key tile
+    const int hq = (kw >> 2) & 1;  // which 64 queries of every query tile
+    const int wq = kw & 3;         // TMEM lane quarter this warp may touch
     const int key = kv0[t] + wq * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float scale = p.scale_log2;
@@ -277,47 +278,53 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       for (int i = i_begin; i < p.nq_tiles; ++i) {
         const int c = i - i_begin;
         const int st = c % kQStages;
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_full[st]), (c / kQStages) & 1, abortp));
-        if (!ok) { if (lane == 0) record_timeout(p.status, 25); break; }
         if (i >= i_start[t]) {
           const int ct = i - i_start[t];
           const int buf = ct & 1;
+          // S^T of this step is complete; its MMAs were issued after Q and the row statistics of
+          // the stage had landed, so this wait covers q_full as well
           ok = __all_sync(0xffffffffu,
                           mbar_wait(smem_u32(&bars.s_full[t][buf]), (ct >> 1) & 1, abortp));
           if (!ok) { if (lane == 0) record_timeout(p.status, 26); break; }
           tc_fence_after_sync();
-          const uint32_t tS = tbase + lane_base + (t * 2 + buf) * 128;
-          // query c of this tile sees `key` iff key <= (i*128 + c) + diag_off
-          const int first_visible = p.causal ? key - p.diag_off - i * kTile : 0;
-          const bool tile_has_mask = p.causal && (kv0[t] + kTile - 1 - p.diag_off > i * kTile);
-          const float4* lse4 = reinterpret_cast<const float4*>(lse_s[st]);
-          // two halves of 64 queries: short enough that every exponential of a half is in flight
-          // at once without crowding the register file
+          const uint32_t tS = tbase + lane_base + (t * 2 + buf) * 128 + hq * 64;
+          const int q_base = i * kTile + hq * 64;
+          // query q of this tile sees `key` iff key <= q + diag_off
+          const int first_visible = p.causal ? key - p.diag_off - q_base : 0;
+          const bool tile_has_mask = p.causal && (kv0[t] + kTile - 1 - p.diag_off > q_base);
+          const float4* lse4 = reinterpret_cast<const float4*>(lse_s[st]) + hq * 16;
+          // two chunks of 32 queries: every exponential of a chunk is in flight at once
 #pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {
-            float s[64];
-            {
-              uint32_t(&u)[64] = *reinterpret_cast<uint32_t(*)[64]>(s);
-              tmem_ld32(tS + hc * 64, *reinterpret_cast<uint32_t(*)[32]>(&u[0]));
-              tmem_ld32(tS + hc * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&u[32]));
-            }
-            float noise[(kMode == 2 || kMode == 4) ? 64 : 1];
+          for (int ch = 0; ch < 2; ++ch) {
+            float s[32];
+            tmem_ld32(tS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(s));
+            float noise[(kMode == 2 || kMode == 4) ? 32 : 1];
             if constexpr (kMode == 2 || kMode == 4) {
 #pragma unroll
-              for (int e = 0; e < 64; ++e) {
-                const int qi = min(i * kTile + hc * 64 + e, p.Sq - 1);
+              for (int e = 0; e < 32; ++e) {
+                const int qi = min(q_base + ch * 32 + e, p.Sq - 1);
                 noise[e] = __ldg(er_col + static_cast<int64_t>(qi) * p.er_sq);
+              }
+              // the operand is read once, straight from HBM: pull the same chunk of the next query
+              // tile into L2 now, so that its loads find it there one step later
+              if (i + 1 < p.nq_tiles) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  const int qi = min(q_base + kTile + ch * 32 + e, p.Sq - 1);
+                  asm volatile("prefetch.global.L2 [%0];" ::"l"(er_col + static_cast<int64_t>(qi) * p.er_sq));
+                }
               }
             }
             tmem_wait_ld();
-            if (hc == 1) {
-              // the whole tile is in registers: the MMA warp may overwrite this TMEM buffer
+            if (ch == 1) {
+              // this thread's part of the tile is in registers; when all 256 have said so the MMA
+              // warp may overwrite the TMEM buffer
               tc_fence_before_sync();
               mbar_arrive(smem_u32(&bars.s_empty[t][buf]));
             }
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {
-              const float4 L = lse4[hc * 16 + g];
+            for (int g = 0; g < 8; ++g) {
+              const float4 L = lse4[ch * 8 + g];
               const float lv[4] = {L.x, L.y, L.z, L.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -326,7 +333,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 if constexpr (kMode == 2) {
                   x = fmaf(s[cc], scale, fmaf(lg2(noise[cc]), -p.inv_tau, -lv[e]));
                 } else if constexpr (kMode == 3) {
-                  const float l2 = seeded_lg2_exp_rand(static_cast<uint32_t>(i * kTile + hc * 64 + cc),
+                  const float l2 = seeded_lg2_exp_rand(static_cast<uint32_t>(q_base + ch * 32 + cc),
                                                        static_cast<uint32_t>(key), head_key);
                   x = fmaf(s[cc], scale, fmaf(l2, -p.inv_tau, -lv[e]));
                 } else {
@@ -337,34 +344,34 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             if (tile_has_mask) {
 #pragma unroll
-              for (int cc = 0; cc < 64; ++cc) s[cc] = (hc * 64 + cc < first_visible) ? 0.f : s[cc];
+              for (int cc = 0; cc < 32; ++cc) s[cc] = (ch * 32 + cc < first_visible) ? 0.f : s[cc];
             }
             if constexpr (kMode == 4) {
 #pragma unroll
-              for (int cc = 0; cc < 64; ++cc)
-                hit = hit || (s[cc] >= noise[cc] && i * kTile + hc * 64 + cc < p.Sq);
+              for (int cc = 0; cc < 32; ++cc) hit = hit || (s[cc] >= noise[cc] && q_base + ch * 32 + cc < p.Sq);
             } else {
 #pragma unroll
-              for (int cc = 0; cc < 64; ++cc) {
+              for (int cc = 0; cc < 32; ++cc) {
                 acc[cc & 3] += s[cc];
                 if constexpr (kMode == 1) acc2[cc & 3] = fmaf(s[cc], s[cc], acc2[cc & 3]);
               }
             }
           }
+        } else {
+          // a step this key tile skips (its keys are invisible to the whole query tile): the stage
+          // may only be released once it has been filled
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_full[st]), (c / kQStages) & 1, abortp));
+          if (!ok) { if (lane == 0) record_timeout(p.status, 25); break; }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars.q_empty[st]));
       }
-      if (ok && key < p.Skv) {
-        const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
-        if constexpr (kMode == 4) {
-          reinterpret_cast<uint8_t*>(p.score)[o] = hit ? 1 : 0;
-        } else {
-          p.score[o] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-        }
-        if constexpr (kMode == 1) p.score_sq[o] = (acc2[0] + acc2[1]) + (acc2[2] + acc2[3]);
-      }
     }
+    // Both query halves leave their parts in shared memory; after the CTA-wide barrier below the
+    // first half's thread adds the two in a fixed order and stores.
+    part_s[0][hq][t][wq * 32 + lane] = kMode == 4 ? (hit ? 1.f : 0.f) : (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    part_s[1][hq][t][wq * 32 + lane] = (acc2[0] + acc2[1]) + (acc2[2] + acc2[3]);
+    if (!ok) *abortp = 1u;
   }
 
   tc_fence_before_sync();
@@ -372,6 +379,21 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tbase, 512);
+  }
+  if (warp >= 4 && ((warp - 4) >> 2 & 1) == 0 && !*abortp) {
+    const int t = (warp - 4) >> 3;
+    const int k_in_tile = (warp & 3) * 32 + lane;
+    const int key = kv0[t] + k_in_tile;
+    if (key < p.Skv) {  // (implies that this key tile is active)
+      const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
+      const float v = part_s[0][0][t][k_in_tile] + part_s[0][1][t][k_in_tile];
+      if constexpr (kMode == 4) {
+        reinterpret_cast<uint8_t*>(p.score)[o] = v != 0.f ? 1 : 0;
+      } else {
+        p.score[o] = v;
+      }
+      if constexpr (kMode == 1) p.score_sq[o] = part_s[1][0][t][k_in_tile] + part_s[1][1][t][k_in_tile];
+    }
   }
 }
 

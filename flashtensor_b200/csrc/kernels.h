@@ -13,6 +13,8 @@ uint32_t* device_status_words();  // device address of a 4-word __device__ array
 void count_launch();
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of per call
 cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
+// error unless the registers the kernel's roles ask for after setmaxnreg fit in what the CTA gets at launch
+cudaError_t check_register_budget(const void* kernel, int threads, int regs_wanted_total);
 
 struct AttnShape {
   int B, H, Sq, Skv;  // H: query heads
