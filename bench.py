@@ -52,7 +52,7 @@ WORKLOADS = {
 
 # DRAM bytes per launch of the attention-forward kernel at the H2O workload, from the ncu capture
 # summarised in profiles/attn_fwd_h2o_c2.md (dram__bytes_read.sum + dram__bytes_write.sum).
-FWD_DRAM_TRAFFIC_BYTES = 161893632
+FWD_DRAM_TRAFFIC_BYTES = 161904640
 
 
 E2E_DEPTH = 2
