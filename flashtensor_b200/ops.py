@@ -5,6 +5,7 @@ current stream without synchronising -- the contract of the reference's generate
 (lib/Translate/to_triton.cpp:579-609).  Shape/dtype problems raise (as the TensorRT back end's
 closure does, python/asuka/backend/tensorrt/builder.py:104-111); nothing falls back to PyTorch.
 """
+import contextlib
 import ctypes
 
 import torch
@@ -25,13 +26,21 @@ def _desc(t):
     raise TypeError(f"unsupported dtype {t.dtype}")
   if t.dim() > 5:
     raise ValueError("at most 5 dimensions")
+  n = t.dim()
   d.ptr = t.data_ptr()
   d.dtype = _DTYPES[t.dtype]
-  d.ndim = t.dim()
-  for i in range(t.dim()):
-    d.shape[i] = t.shape[i]
-    d.stride[i] = t.stride(i)
+  d.ndim = n
+  d.shape[:n] = t.shape      # (slice assignment: one call instead of a Python loop; this function
+  d.stride[:n] = t.stride()  #  is most of the host time of a call at small shapes)
   return d
+
+
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def _on(dev):
+  """Context that makes `dev` the current CUDA device (a no-op, and cheap, when it already is)."""
+  return _NO_SWITCH if dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
 
 
 def _stream(t):
@@ -64,7 +73,7 @@ def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
   _same_device(q4, k4, v4)
-  with torch.cuda.device(q4.device):
+  with _on(q4.device):
     if out is None:
       out = torch.empty(q4.shape, dtype=q4.dtype, device=q4.device)
     lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32,
@@ -85,7 +94,7 @@ def col_scores(q, k, lse, mode=_lib.SCORE_SUM, causal=True, softmax_scale=0.0, e
   q4, k4 = _as4d(q), _as4d(k)
   _same_device(q4, k4, lse, exp_rand, corm_mask)
   B, Skv, H = k4.shape[0], k4.shape[1], k4.shape[2]
-  with torch.cuda.device(q4.device):
+  with _on(q4.device):
     score = torch.empty((B, H, Skv), dtype=torch.bool if mode == _lib.SCORE_CORM else torch.float32,
                         device=q4.device)
     score_sq = torch.empty_like(score) if mode == _lib.SCORE_SUM_SQ else None
@@ -101,7 +110,7 @@ def keyformer_rowstat(q, k, causal=True, softmax_scale=0.0, exp_rand=None, tau=1
   lib = _lib.load()
   q4, k4 = _as4d(q), _as4d(k)
   _same_device(q4, k4, exp_rand)
-  with torch.cuda.device(q4.device):
+  with _on(q4.device):
     lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32, device=q4.device)
     p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _lib.Tensor(), _lib.Tensor(),
                          _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
@@ -117,7 +126,7 @@ def select_topk(score, k_keep, mode=_lib.SELECT_TOPK, recent=0, score_sq=None, q
   _same_device(score, score_sq)
   B, H, _ = score.shape
   n_out = k_keep + (recent if mode == _lib.SELECT_TOPK_RECENT else 0)
-  with torch.cuda.device(score.device):
+  with _on(score.device):
     idx = torch.empty((B, H, n_out), dtype=torch.int32, device=score.device)
     p = _lib.SelectParams(_desc(score), _desc(score_sq), _desc(idx), int(k_keep), int(recent),
                           int(q_len), int(mode))
@@ -129,7 +138,7 @@ def pool_scores(score, kernel_size):
   """SnapKV smoothing: avg_pool1d(score, kernel_size, padding=kernel_size // 2, stride=1) over keys."""
   lib = _lib.load()
   _same_device(score)
-  with torch.cuda.device(score.device):
+  with _on(score.device):
     out = torch.empty_like(score)
     a, b = _desc(score), _desc(out)
     _lib.check("asuka_b200_pool_scores",
@@ -143,7 +152,7 @@ def gather_kv(k, v, idx):
   _same_device(k, v, idx)
   B, _, H, D = k.shape
   n = idx.shape[2]
-  with torch.cuda.device(k.device):
+  with _on(k.device):
     k_out = torch.empty((B, n, H, D), dtype=k.dtype, device=k.device)
     v_out = torch.empty_like(k_out)
     p = _lib.GatherParams(_desc(k), _desc(v), _desc(idx), _desc(k_out), _desc(v_out))
@@ -156,7 +165,7 @@ def sima_fwd(q, k, v, out_dtype=None):
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
   _same_device(q4, k4, v4)
-  with torch.cuda.device(q4.device):
+  with _on(q4.device):
     out = torch.empty(q4.shape, dtype=out_dtype or q4.dtype, device=q4.device)
     p = _lib.SimaParams(_desc(q4), _desc(k4), _desc(v4), _desc(out))
     nbytes = ctypes.c_size_t(0)
@@ -177,7 +186,7 @@ def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None,
   # scores and indices are per key/value head (with grouped-query attention: the group mean)
   B, Skv, H = k4.shape[0], k4.shape[1], k4.shape[2]
   dev = q4.device
-  with torch.cuda.device(dev):
+  with _on(dev):
     if out is None:
       out = torch.empty(q4.shape, dtype=q4.dtype, device=dev)
     if score is None:
@@ -217,7 +226,7 @@ def h2o_static(q, k, v, out, score, idx=None, causal=True, softmax_scale=0.0, k_
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
   _same_device(q4, k4, v4, out, score, idx)
-  with torch.cuda.device(q4.device):
+  with _on(q4.device):
     p = _lib.CaseParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(score),
                         _lib.Tensor(), _lib.Tensor(), _desc(idx), float(softmax_scale), 1.0, 0,
                         int(bool(causal)), int(k_keep), int(recent))
