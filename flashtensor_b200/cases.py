@@ -58,6 +58,39 @@ class _Case:
     v = torch.randn(shape_kv, dtype=dtype, device=device)
     return {"input": {"q": q, "k": k, "v": v}, "output": list(self.output_names)}
 
+  # ---- the bookkeeping the reference's Kernel object carries (python/asuka/partition/kernel.py)
+  @property
+  def input_names(self):
+    """Positional input order of the callable (Kernel.inputs, kernel.py:78-93)."""
+    return list(self.prepare(1, 8, 8, device="cpu")["input"].keys())
+
+  def get_flops(self, batch_size=1, q_len=4096, kv_len=4096):
+    """Dense flop count of the case's contractions, 2*m*k*n per dot with no credit for the causal
+    mask -- the convention of Kernel.get_flops (kernel.py:155-159).  The algorithmic count the
+    benchmark reports (unmasked region only) is utils.causal_flops."""
+    return 4 * batch_size * self.head_num * q_len * kv_len * self.head_dim
+
+  def get_mem_size(self, batch_size=1, q_len=4096, kv_len=4096):
+    """Elements (not bytes) of all inputs and outputs, as Kernel.get_mem_size (kernel.py:161-175)."""
+    ins = self.prepare(1, 8, 8, device="cpu")["input"]
+    n = 0
+    for name in ins:
+      if name in ("q",):
+        n += batch_size * q_len * self.head_num * self.head_dim
+      elif name in ("k", "v"):
+        n += batch_size * kv_len * self.kv_head_num * self.head_dim
+      elif name == "exp_rand":
+        n += batch_size * self.head_num * q_len * kv_len
+      elif name == "corm_mask":
+        n += q_len * kv_len
+    n += batch_size * q_len * self.head_num * self.head_dim                      # out
+    n += (len(self.output_names) - 1) * batch_size * self.kv_head_num * kv_len   # per-key outputs
+    return n
+
+  def prepare_dummy_inputs(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):
+    """Positional list of random inputs, as Kernel.prepare_dummy_inputs (kernel.py:181-195)."""
+    return list(self.prepare(batch_size, q_len, kv_len, dtype, device)["input"].values())
+
 
 class Attn(_Case):
   """cases/kernels/attn.py:7-34.  ``causal=False`` gives ``forward_wo_mask`` of cases/attn.py;
@@ -208,6 +241,10 @@ class SimA(_Case):
   def forward(self, q, k, v):
     self._check(q)
     return ops.sima_fwd(q, k, v)
+
+  def get_flops(self, batch_size=8, q_len=8192, kv_len=None):
+    """K^T V and Q M: 2 * S * D * D each per (batch, head)."""
+    return 4 * batch_size * self.head_num * q_len * self.head_dim * self.head_dim
 
   def prepare(self, batch_size=8, q_len=8192, kv_len=None, dtype=torch.float16, device=None):
     ret = super().prepare(batch_size, q_len, q_len, dtype, device)

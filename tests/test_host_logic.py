@@ -190,3 +190,20 @@ def test_two_rank_sharding_over_gloo(tmp_path):
   for r, (p, o) in enumerate(zip(procs, outs)):
     assert p.returncode == 0, o
     assert f"ok {r}" in o
+
+
+def test_case_bookkeeping_like_the_reference_kernel_object():
+  # python/asuka/partition/kernel.py: positional inputs, dense flops (2*m*k*n per dot), sizes in elements
+  import flashtensor_b200 as ft
+  h2o = ft.H2O(head_num=32, kv_head_num=32)
+  assert h2o.input_names == ["q", "k", "v"] and h2o.output_names == ["out", "h2o_score"]
+  assert h2o.get_flops(1, 4096, 4096) == 274877906944           # 274.9 GF dense at the H2O configuration
+  assert ft.RoCo(head_num=40, kv_head_num=40).get_flops(2, 4096, 4096) == 687194767360
+  assert ft.Attn().get_flops(1, 1024, 1024) == 17179869184
+  assert ft.SimA().get_flops(8, 8192) == 4 * 8 * 32 * 8192 * 128 * 128
+  assert h2o.get_mem_size(1, 4096, 4096) == 4 * 4096 * 32 * 128 + 32 * 4096
+  kf = ft.KeyFormer()
+  assert kf.input_names == ["q", "k", "v", "exp_rand"]
+  assert kf.get_mem_size(4, 2048, 2048) == 4 * 4 * 2048 * 32 * 128 + 4 * 32 * 2048 * 2048 + 4 * 32 * 2048
+  args = ft.H2O(head_num=4, kv_head_num=2).prepare_dummy_inputs(2, 16, 24, device="cpu")
+  assert [tuple(a.shape) for a in args] == [(2, 16, 4, 128), (2, 24, 2, 128), (2, 24, 2, 128)]
