@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused-attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--case h2o|attn|roco|keyformer|sima]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--case h2o|attn|roco|keyformer|keyformer_seeded|sima|ea]
     python bench.py --impl reference ...      # the reference's CPU eager path on the host cores
 
 One "step" is one call of the case on one batch of synthetic inputs.  The default workload is the
@@ -48,7 +48,9 @@ WORKLOADS = {
     "roco": dict(B=2, H=40, S=4096, dtype="bf16", k_keep=512,
                  desc="RoCo prefill bf16 B2 H40 S4096 D128, top-k S/8 by mean then std"),
     "sima": dict(B=8, H=32, S=8192, dtype="f16", desc="SimA fp16 B8 H32 S8192 D128 non-causal"),
+    "ea": dict(B=8, H=32, S=8192, dtype="f16", desc="EA fp16 B8 H32 S8192 D128 (softmax over features of q, over the sequence of k)"),
 }
+STREAMING = ("sima", "ea")   # HBM-bound two-pass programs: no S x S product
 
 # DRAM bytes per launch of the attention-forward kernel at the H2O workload, from the ncu capture
 # summarised in profiles/attn_fwd_h2o_c2.md (dram__bytes_read.sum + dram__bytes_write.sum).
@@ -72,7 +74,7 @@ def peaks():
 
 def flops_of(case, w, batch):
   from flashtensor_b200 import utils
-  if case == "sima":
+  if case in STREAMING:
     return utils.sima_flops(batch, w["H"], w["S"])
   return utils.causal_flops(batch, w["H"], w["S"], w["S"])
 
@@ -179,7 +181,7 @@ def build_step(case, w):
   if case == "keyformer_seeded":
     m = ft.KeyFormer(tau=w["tau"], head_num=H, kv_head_num=H)
     return lambda q, k, v: m.seeded(q, k, v, w["seed"], w["k_keep"])
-  m = ft.SimA(head_num=H, kv_head_num=H)
+  m = (ft.EA if case == "ea" else ft.SimA)(head_num=H, kv_head_num=H)
   return lambda q, k, v: (m(q, k, v),)
 
 
@@ -206,7 +208,7 @@ def cpu_oracle_sample(case, w, heads, threads):
   from oracle import attn_oracle as O
   torch.set_num_threads(threads)
   dtype = torch.float16 if w["dtype"] == "f16" else torch.bfloat16
-  ins = O.make_inputs("sima" if case == "sima" else ("keyformer" if case == "keyformer" else "h2o"),
+  ins = O.make_inputs("sima" if case in STREAMING else ("keyformer" if case == "keyformer" else "h2o"),
                       1, w["S"], w["S"], heads, 128, dtype, seed=0)
   ins = [t.float() for t in ins]
   t0 = time.time()
@@ -223,11 +225,13 @@ def cpu_oracle_sample(case, w, heads, threads):
       ins = ins[:3] + [O.keyformer_seeded_exp_rand(w["seed"], 1, heads, w["S"], w["S"])]
     _, s = O.keyformer(*ins, tau=w["tau"])
     O.keyformer_select(s.numpy(), w["k_keep"])
+  elif case == "ea":
+    O.ea(*ins)
   else:
     O.sima(*ins)
   dt = time.time() - t0
   from flashtensor_b200 import utils
-  fl = utils.sima_flops(1, heads, w["S"]) if case == "sima" else utils.causal_flops(1, heads, w["S"], w["S"])
+  fl = utils.sima_flops(1, heads, w["S"]) if case in STREAMING else utils.causal_flops(1, heads, w["S"], w["S"])
   return dt, fl
 
 
@@ -360,11 +364,12 @@ def main():
 
   # ---- (3) the dominant kernel alone, for the roofline -------------------------------------
   pk = peaks()
-  if args.case == "sima":
-    ms_k, t0, t1 = ms, None, None          # SimA is one HBM-bound pipeline: the step is the kernel chain
+  if args.case in STREAMING:
+    ms_k, t0, t1 = ms, None, None          # one HBM-bound pipeline: the step is the kernel chain
     algo = io_bytes_of(args.case, w, batch)
     achieved = algo / (ms_per_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "sima_stats + sima_reduce + sima_out (whole step)",
+    roofline = {"bound": "hbm", "kernel": ("ea_colmax + " if args.case == "ea" else "") +
+                "sima_stats + sima_reduce + sima_out (whole step)",
                 "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                 "algorithmic_bytes_per_launch": algo}

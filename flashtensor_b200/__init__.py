@@ -4,7 +4,7 @@ per-case callables and back-end plug-in interface.  The CUDA library is mandator
 operator layer without it raises."""
 from . import _lib
 from .builder import B200Builder, Builder
-from .cases import CASES, Attn, Corm, Gemma2, H2O, KeyFormer, RoCo, SimA, SnapKV, get_model
+from .cases import CASES, EA, Attn, Corm, Gemma2, H2O, KeyFormer, RoCo, SimA, SnapKV, get_model
 
-__all__ = ["Attn", "Gemma2", "SnapKV", "Corm", "H2O", "KeyFormer", "RoCo", "SimA", "CASES", "get_model", "Builder",
+__all__ = ["EA", "Attn", "Gemma2", "SnapKV", "Corm", "H2O", "KeyFormer", "RoCo", "SimA", "CASES", "get_model", "Builder",
            "B200Builder", "_lib"]

@@ -79,6 +79,7 @@ SYMBOLS = {
     "asuka_b200_gather_kv": (ctypes.c_int, [ctypes.POINTER(GatherParams), ctypes.c_void_p]),
     "asuka_b200_sima_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_sima_fwd": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "asuka_b200_ea_fwd": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_case_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_h2o": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_h2o_static": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.c_void_p]),

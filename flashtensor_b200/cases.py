@@ -253,7 +253,18 @@ class SimA(_Case):
     return ret
 
 
-CASES = {"Attn": Attn, "Gemma2": Gemma2, "SnapKV": SnapKV, "Corm": Corm, "H2O": H2O, "KeyFormer": KeyFormer, "RoCo": RoCo, "SimA": SimA}
+class EA(SimA):
+  """bench/ea.mlir:13-17: out = softmax(q over features) (softmax(k over the sequence)^T v)."""
+
+  def forward(self, q, k, v):
+    self._check(q)
+    return ops.ea_fwd(q, k, v)
+
+  def prepare(self, batch_size=8, q_len=8192, kv_len=None, dtype=torch.float16, device=None):
+    return _Case.prepare(self, batch_size, q_len, q_len, dtype, device)
+
+
+CASES = {"EA": EA, "Attn": Attn, "Gemma2": Gemma2, "SnapKV": SnapKV, "Corm": Corm, "H2O": H2O, "KeyFormer": KeyFormer, "RoCo": RoCo, "SimA": SimA}
 
 
 def get_model(name="H2O", **kwargs):

@@ -335,14 +335,16 @@ int prep_sima(const asuka_sima_params* p, SimaShape* sh) {
   sh->H = static_cast<int>(p->q.shape[2]);
   sh->bf16 = p->q.dtype == ASUKA_BF16;
   sh->out_f32 = p->out.dtype == ASUKA_F32;
+  sh->ea = false;
   if (static_cast<int64_t>(sh->B) * sh->H > (1 << 20)) return ASUKA_ERR_TOO_LARGE;
   return ASUKA_OK;
 }
 
-int sima_impl(const asuka_sima_params* p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+int sima_impl(const asuka_sima_params* p, void* ws, size_t ws_bytes, cudaStream_t stream, bool ea) {
   SimaShape sh;
   int r = prep_sima(p, &sh);
   if (r != ASUKA_OK) return r;
+  sh.ea = ea;
   if (sh.out_f32) {
     const asuka_tensor& o = p->out;
     if (o.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
@@ -370,7 +372,8 @@ int sima_impl(const asuka_sima_params* p, void* ws, size_t ws_bytes, cudaStream_
     mo = mq;
   }
   return map_cuda(launch_sima(mq, mk, mv, mo, p->out.ptr, p->out.stride[0], p->out.stride[1],
-                              p->out.stride[2], ws, sh, stream));
+                              p->out.stride[2], ws, sh, p->k.ptr, p->k.stride[0], p->k.stride[1],
+                              p->k.stride[2], stream));
 }
 
 // forward + column scores (+ selection) on one stream; the row statistic lives in `ws`
@@ -644,7 +647,11 @@ int asuka_b200_sima_workspace_bytes(const asuka_sima_params* p, size_t* bytes) {
 }
 
 int asuka_b200_sima_fwd(const asuka_sima_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
-  return sima_impl(p, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+  return sima_impl(p, ws, ws_bytes, static_cast<cudaStream_t>(stream), false);
+}
+
+int asuka_b200_ea_fwd(const asuka_sima_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
+  return sima_impl(p, ws, ws_bytes, static_cast<cudaStream_t>(stream), true);
 }
 
 int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes) {

@@ -78,11 +78,13 @@ struct SimaShape {
   int B, H, S;
   bool bf16;
   bool out_f32;
+  bool ea;  // the EA program (softmax normalisations) instead of SimA (L1 normalisations)
 };
 size_t sima_workspace_bytes(const SimaShape& s);
 cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                         const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
                         int64_t out_stride_s, int64_t out_stride_h, void* ws, const SimaShape& s,
+                        const void* k_ptr, int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
                         cudaStream_t stream);
 
 }  // namespace asuka

@@ -43,6 +43,7 @@ struct SimaWs {
   float* part_c;     // [BH][nchunks][2][128] partial ck, cq
   uint16_t* m16;     // [BH][e][d] scaled M'^T in the input type
   float* inv_scale;  // [BH][4]: one per block of 32 output channels
+  float* part_cmax;  // [BH][nchunks][128] EA only: partial column maxima of K over the sequence
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -55,12 +56,16 @@ constexpr uint32_t kStSmem = kStStages * 3 * kTileBytes + 1024;
 struct StatsParams {
   int B, H, S;
   int nchunks, tiles_per_chunk, ntiles;
+  int ea;            // 1: the EA program (softmax normalisations), 0: SimA (L1 normalisations)
+  const uint16_t* k; // EA only: K [B,S,H,128] for the column-maximum pre-pass, strides in elements
+  int64_t k_sb, k_ss, k_sh;
   SimaWs ws;
   uint32_t* status;
 };
 
 struct StBars {
   uint64_t full[kStStages], empty[kStStages], m_done;
+  uint64_t ktrans[kStStages];  // EA only: the K tile of the stage has been exponentiated in place
 };
 
 template <bool kBF16>
@@ -80,12 +85,96 @@ __device__ __forceinline__ void abs_acc8(const uint4& v, float (&acc)[8]) {
 }
 
 template <bool kBF16>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t;
+    if constexpr (kBF16) {
+      t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    } else {
+      t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    }
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+// rounds to the 16-bit type; `f` is overwritten with the rounded values
+template <bool kBF16>
+__device__ __forceinline__ uint4 pack8(float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (kBF16) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+      const float2 r = __bfloat1622float2(t);
+      f[2 * i] = r.x;
+      f[2 * i + 1] = r.y;
+    } else {
+      __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+      const float2 r = __half22float2(t);
+      f[2 * i] = r.x;
+      f[2 * i + 1] = r.y;
+    }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------------------------
+// 0. (EA only) column maxima of K over a slab of the sequence: softmax over the sequence axis
+//    (bench/ea.mlir:14) needs them before any exponential is taken.  Plain coalesced 16-byte
+//    loads; one partial per slab, reduced by the statistics kernel.
+// ---------------------------------------------------------------------------------------------
+template <bool kBF16>
+__global__ void __launch_bounds__(256, 4) ea_colmax_kernel(const StatsParams p) {
+  __shared__ float red[16][kTile];
+  const int tid = threadIdx.x;
+  const int chunk = static_cast<int>(blockIdx.x) % p.nchunks;
+  const int bh = static_cast<int>(blockIdx.x) / p.nchunks;
+  const int b = bh / p.H, h = bh % p.H;
+  const int chunk16 = tid & 15, rg = tid >> 4;
+  const int row0 = chunk * p.tiles_per_chunk * kTile;
+  const int row1 = min(p.S, row0 + p.tiles_per_chunk * kTile);
+  const uint16_t* base = p.k + static_cast<int64_t>(b) * p.k_sb + static_cast<int64_t>(h) * p.k_sh + chunk16 * 8;
+  float mx[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+  for (int r = row0 + rg; r < row1; r += 16) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + static_cast<int64_t>(r) * p.k_ss));
+    float f[8];
+    unpack8<kBF16>(v, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx[i] = fmaxf(mx[i], f[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rg][chunk16 * 8 + i] = mx[i];
+  __syncthreads();
+  if (tid < kTile) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < 16; ++g) m = fmaxf(m, red[g][tid]);
+    p.ws.part_cmax[(static_cast<size_t>(bh) * p.nchunks + chunk) * kTile + tid] = m;
+  }
+}
+
+// kEA: the EA program.  K is exponentiated in place in shared memory against the column maxima
+// before the MMA reads it (so the product is exp(K - max)^T V and the column sums are the softmax
+// denominators); Q is not needed in this pass.
+template <bool kBF16, bool kEA>
 __global__ void __launch_bounds__(kStThreads, 1)
 sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const StatsParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) StBars bars;
   __shared__ float red[2][8][kTile];
+  __shared__ float cmax_s[kTile];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -106,7 +195,17 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       mbar_init(smem_u32(&bars.empty[i]), 1 + 8);
     }
     mbar_init(smem_u32(&bars.m_done), 1);
+    for (int i = 0; i < kStStages; ++i) mbar_init(smem_u32(&bars.ktrans[i]), 256);
     mbar_fence_init();
+  }
+  if constexpr (kEA) {
+    if (tid >= 128 && tid < 256) {  // column maxima of the whole sequence: reduce every slab's partial
+      const int d = tid - 128;
+      const float* pc = p.ws.part_cmax + static_cast<size_t>(blockIdx.x / p.nchunks) * p.nchunks * kTile + d;
+      float m = -INFINITY;
+      for (int c = 0; c < p.nchunks; ++c) m = fmaxf(m, pc[c * kTile]);
+      cmax_s[d] = m;
+    }
   }
   if (warp == 1) {
     __syncwarp();
@@ -131,13 +230,15 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t bar = smem_u32(&bars.full[st]);
         const uint32_t base = smem_base + st * 3 * kTileBytes;
         const int s0 = (tile0 + i) * kTile;
-        mbar_expect_tx(bar, 3 * kTileBytes);
+        mbar_expect_tx(bar, (kEA ? 2 : 3) * kTileBytes);
         tma_load_4d(base, &map_k, bar, 0, h, s0, b);
         tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h, s0, b);
         tma_load_4d(base + kTileBytes, &map_v, bar, 0, h, s0, b);
         tma_load_4d(base + kTileBytes + kHalfBytes, &map_v, bar, 64, h, s0, b);
-        tma_load_4d(base + 2 * kTileBytes, &map_q, bar, 0, h, s0, b);
-        tma_load_4d(base + 2 * kTileBytes + kHalfBytes, &map_q, bar, 64, h, s0, b);
+        if constexpr (!kEA) {
+          tma_load_4d(base + 2 * kTileBytes, &map_q, bar, 0, h, s0, b);
+          tma_load_4d(base + 2 * kTileBytes + kHalfBytes, &map_q, bar, 64, h, s0, b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -150,6 +251,10 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int st = i % kStStages;
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp));
         if (!ok) { if (lane == 0) record_timeout(p.status, 42); break; }
+        if constexpr (kEA) {
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.ktrans[st]), (i / kStStages) & 1, abortp));
+          if (!ok) { if (lane == 0) record_timeout(p.status, 45); break; }
+        }
         tc_fence_after_sync();
         const uint32_t base = smem_base + st * 3 * kTileBytes;
         // M = K^T V: TMEM lane = d, column = e
@@ -180,21 +285,54 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const int st = i % kStStages;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 43); break; }
-      const uint8_t* tile = smem_gen + st * 3 * kTileBytes + (which ? 2 * kTileBytes : 0) +
-                            (chunk16 >> 3) * kHalfBytes;
+      if constexpr (kEA) {
+        // all 256 threads work on the K tile: rows 16 apart per thread; k' = exp(k - colmax),
+        // rounded to the input type and written back for the MMA; rows past the sequence give 0
+        uint8_t* tile = smem_gen + st * 3 * kTileBytes + (chunk16 >> 3) * kHalfBytes;
+        const int rg16 = which * 8 + rg;
+        const int s0 = (tile0 + i) * kTile;
+        float cm[8];
 #pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        const int row = rg + 8 * r;
-        const uint4 v = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
-        abs_acc8<kBF16>(v, acc);
+        for (int e = 0; e < 8; ++e) cm[e] = cmax_s[chunk16 * 8 + e] * 1.4426950408889634f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const int row = rg16 + 16 * r;
+          uint4* ptr = reinterpret_cast<uint4*>(tile + sw128_offset(row, chunk16 & 7));
+          float f[8];
+          unpack8<kBF16>(*ptr, f);
+          const bool live = s0 + row < p.S;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = live ? ex2_approx(fmaf(f[e], 1.4426950408889634f, -cm[e])) : 0.f;
+          *ptr = pack8<kBF16>(f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += f[e];
+        }
+        fence_proxy_async_smem();  // written by ordinary stores, read by the tensor pipe
+        mbar_arrive(smem_u32(&bars.ktrans[st]));
+      } else {
+        const uint8_t* tile = smem_gen + st * 3 * kTileBytes + (which ? 2 * kTileBytes : 0) +
+                              (chunk16 >> 3) * kHalfBytes;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          const int row = rg + 8 * r;
+          const uint4 v = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
+          abs_acc8<kBF16>(v, acc);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) red[which][rg][chunk16 * 8 + i] = acc[i];
-    named_bar_sync(1 + which, 128);
-    {
+    if constexpr (kEA) {
+      named_bar_sync(1, 256);
+      float s = 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) s += red[0][g][t128] + red[1][g][t128];
+      // slot 0: the softmax denominators' partial; slot 1 (SimA's sum|Q|) is not used by EA
+      p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + which) * kTile + t128] = which ? 1.f : s;
+    } else {
+      named_bar_sync(1 + which, 128);
       float s = 0.f;
 #pragma unroll
       for (int g = 0; g < 8; ++g) s += red[which][g][t128];
@@ -259,7 +397,7 @@ __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p
       ck += pc[(c * 2 + 0) * kTile + tid];
       cq += pc[(c * 2 + 1) * kTile + tid];
     }
-    inv_c[tid] = __fdiv_rn(1.0f, __fmul_rn(ck, cq));
+    inv_c[tid] = p.ea ? __fdiv_rn(1.0f, ck) : __fdiv_rn(1.0f, __fmul_rn(ck, cq));
   }
   __syncthreads();
   float vals[kRedElems / 256];
@@ -326,14 +464,19 @@ struct OutParams {
 
 struct OutBars {
   uint64_t m_full, q_full[kOutStages], q_empty[kOutStages], acc_full[2], acc_empty[2];
+  uint64_t qtrans[kOutStages];  // EA only: the Q tile of the stage has been exponentiated in place
 };
 
-template <bool kBF16, bool kOutF32>
-__global__ void __launch_bounds__(kOutThreads, 1)
+// kEA: softmax over the features of every query row (bench/ea.mlir:13): the row's thread
+// exponentiates it in place in shared memory against the row maximum before the MMA reads it, and
+// divides by the row sum in the epilogue (the same thread owns the row's accumulator lane).
+template <bool kBF16, bool kOutF32, bool kEA>
+__global__ void __launch_bounds__(kOutThreads + (kEA ? 256 : 0), 1)  // EA: warps 8-15 exponentiate Q
 sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_m,
                 const __grid_constant__ CUtensorMap map_o, const OutParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) OutBars bars;
+  __shared__ float inv_r_s[kOutStages + 2][kTile];  // EA: 1 / row sum of the exponentiated Q rows, ring over tiles
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -361,6 +504,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(smem_u32(&bars.acc_full[i]), 1);
       mbar_init(smem_u32(&bars.acc_empty[i]), 128);
     }
+    for (int i = 0; i < kOutStages; ++i) mbar_init(smem_u32(&bars.qtrans[i]), 256);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -409,6 +553,10 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int st = i % kOutStages, buf = i & 1;
         ok = wait_all(&bars.q_full[st], (i / kOutStages) & 1, 53);
         if (!ok) break;
+        if constexpr (kEA) {
+          ok = wait_all(&bars.qtrans[st], (i / kOutStages) & 1, 56);
+          if (!ok) break;
+        }
         if (i >= 2) {
           ok = wait_all(&bars.acc_empty[buf], ((i >> 1) - 1) & 1, 54);
           if (!ok) break;
@@ -427,7 +575,51 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         __syncwarp();
       }
     }
-  } else if (warp >= 4) {
+  } else if (kEA && warp >= 8) {
+    // ------------------------------------------------------------- EA: softmax numerators of Q
+    // Two threads per row (adjacent lanes, 64 features each) exponentiate every Q tile in place
+    // against the row maximum and leave 1 / (sum of the rounded values) for the epilogue thread
+    // of the row.  Two warps per scheduler: one alone issues an ex2 only every ~11 clk.
+    const int t256 = tid - 256;
+    const int r = t256 >> 1, half = t256 & 1;
+    bool ok = true;
+    for (int i = 0; i < ntile && ok; ++i) {
+      const int st = i % kOutStages;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_full[st]), (i / kOutStages) & 1, abortp));
+      if (!ok) { if (lane == 0) record_timeout(p.status, 57); break; }
+      uint8_t* tile = smem_gen + (sQ - smem_base) + st * kTileBytes + half * kHalfBytes;
+      uint4 raw[8];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        raw[c] = *reinterpret_cast<const uint4*>(tile + sw128_offset(r, c));
+        float f[8];
+        unpack8<kBF16>(raw[c], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx = fmaxf(mx, f[e]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      const float neg = -mx * 1.4426950408889634f;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float f[8];
+        unpack8<kBF16>(raw[c], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = ex2_approx(fmaf(f[e], 1.4426950408889634f, neg));
+        *reinterpret_cast<uint4*>(tile + sw128_offset(r, c)) = pack8<kBF16>(f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += f[e];
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      // The slot last held tile i - 5.  This tile's Q landed only after the MMA of tile i - 3 had
+      // retired, that MMA was issued only after the epilogue of tile i - 5 had released its
+      // accumulator, and the epilogue reads its 1/sum before it does that.
+      if (half == 0) inv_r_s[i % (kOutStages + 2)][r] = 1.f / sum;
+      fence_proxy_async_smem();  // the tile was written by ordinary stores, the tensor pipe reads it
+      mbar_arrive(smem_u32(&bars.qtrans[st]));
+    }
+  } else if (warp >= 4 && warp < 8) {
     const int wq = warp & 3;
     const int r = wq * 32 + lane;  // row of the tile
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
@@ -435,12 +627,13 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const float inv4[4] = {p.inv_scale[bh * 4 + 0], p.inv_scale[bh * 4 + 1], p.inv_scale[bh * 4 + 2],
                            p.inv_scale[bh * 4 + 3]};
     bool ok = true;
-    for (int i = 0; i < ntile; ++i) {
+    for (int i = 0; i < ntile && ok; ++i) {
       const int buf = i & 1;
       const int s0 = (tile0 + i) * kTile;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_full[buf]), (i >> 1) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 55); break; }
       tc_fence_after_sync();
+      const float inv_r = kEA ? inv_r_s[i % (kOutStages + 2)][r] : 1.f;
       // the staging buffer about to be overwritten must have been read by its previous store
       if constexpr (!kOutF32) {
         if (tid == 128) tma_store_wait_read_n<1>();
@@ -452,7 +645,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         uint32_t u[32];
         tmem_ld32(tbase + lane_base + buf * 128 + c * 32, u);
         tmem_wait_ld();
-        const float inv_sc = inv4[c];
+        const float inv_sc = kEA ? inv4[c] * inv_r : inv4[c];
         if constexpr (kOutF32) {
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
@@ -528,7 +721,7 @@ size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 struct Plan {
   int ntiles, nchunks, tiles_per_chunk;
-  size_t off_pm, off_pc, off_m16, off_sc, total;
+  size_t off_pm, off_pc, off_m16, off_sc, off_cmax, total;
 };
 
 Plan make_plan(const SimaShape& s) {
@@ -546,6 +739,7 @@ Plan make_plan(const SimaShape& s) {
   pl.off_pc = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * 2 * kTile * 4);
   pl.off_m16 = off; off = align256(off + static_cast<size_t>(bh) * kMElems * 2);
   pl.off_sc = off; off = align256(off + static_cast<size_t>(bh) * kRedBlocks * 4);
+  pl.off_cmax = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * kTile * 4);
   pl.total = off;
   return pl;
 }
@@ -557,6 +751,7 @@ size_t sima_workspace_bytes(const SimaShape& s) { return make_plan(s).total; }
 cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                         const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
                         int64_t out_stride_s, int64_t out_stride_h, void* ws, const SimaShape& s,
+                        const void* k_ptr, int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
                         cudaStream_t stream) {
   const Plan pl = make_plan(s);
   const int bh = s.B * s.H;
@@ -568,11 +763,23 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   sp.ws.part_c = reinterpret_cast<float*>(w + pl.off_pc);
   sp.ws.m16 = reinterpret_cast<uint16_t*>(w + pl.off_m16);
   sp.ws.inv_scale = reinterpret_cast<float*>(w + pl.off_sc);
+  sp.ws.part_cmax = reinterpret_cast<float*>(w + pl.off_cmax);
+  sp.ea = s.ea ? 1 : 0;
+  sp.k = static_cast<const uint16_t*>(k_ptr);
+  sp.k_sb = k_stride_b; sp.k_ss = k_stride_s; sp.k_sh = k_stride_h;
   sp.status = device_status_words();
 
   cudaError_t e;
+  if (s.ea) {
+    auto kern = s.bf16 ? ea_colmax_kernel<true> : ea_colmax_kernel<false>;
+    kern<<<static_cast<unsigned>(bh) * pl.nchunks, 256, 0, stream>>>(sp);
+    count_launch();
+    if ((e = cudaPeekAtLastError()) != cudaSuccess) return e;
+  }
   {
-    auto kern = s.bf16 ? sima_stats_kernel<true> : sima_stats_kernel<false>;
+    void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, StatsParams);
+    if (s.ea) kern = s.bf16 ? sima_stats_kernel<true, true> : sima_stats_kernel<false, true>;
+    else kern = s.bf16 ? sima_stats_kernel<true, false> : sima_stats_kernel<false, false>;
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kStSmem);
     if (e != cudaSuccess) return e;
     kern<<<static_cast<unsigned>(bh) * pl.nchunks, kStThreads, kStSmem, stream>>>(mq, mk, mv, sp);
@@ -604,11 +811,16 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     op.o_sb = out_stride_b; op.o_ss = out_stride_s; op.o_sh = out_stride_h;
     op.status = sp.status;
     void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, OutParams);
-    if (s.out_f32) kern = s.bf16 ? sima_out_kernel<true, true> : sima_out_kernel<false, true>;
-    else kern = s.bf16 ? sima_out_kernel<true, false> : sima_out_kernel<false, false>;
+    if (s.ea) {
+      if (s.out_f32) kern = s.bf16 ? sima_out_kernel<true, true, true> : sima_out_kernel<false, true, true>;
+      else kern = s.bf16 ? sima_out_kernel<true, false, true> : sima_out_kernel<false, false, true>;
+    } else {
+      if (s.out_f32) kern = s.bf16 ? sima_out_kernel<true, true, false> : sima_out_kernel<false, true, false>;
+      else kern = s.bf16 ? sima_out_kernel<true, false, false> : sima_out_kernel<false, false, false>;
+    }
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kOutSmem);
     if (e != cudaSuccess) return e;
-    kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads, kOutSmem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);
+    kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads + (s.ea ? 256 : 0), kOutSmem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);
     count_launch();
     e = cudaPeekAtLastError();
   }

@@ -160,7 +160,7 @@ def gather_kv(k, v, idx):
   return k_out, v_out
 
 
-def sima_fwd(q, k, v, out_dtype=None):
+def sima_fwd(q, k, v, out_dtype=None, _entry="asuka_b200_sima_fwd"):
   """SimA: out = L1norm_seq(q) (L1norm_seq(k)^T v), [B,S,H,128]."""
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
@@ -172,10 +172,14 @@ def sima_fwd(q, k, v, out_dtype=None):
     _lib.check("asuka_b200_sima_workspace_bytes",
                lib.asuka_b200_sima_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)))
     ws = torch.empty((max(nbytes.value, 16),), dtype=torch.uint8, device=q4.device)
-    _lib.check("asuka_b200_sima_fwd",
-               lib.asuka_b200_sima_fwd(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()),
-                                       ctypes.c_size_t(ws.numel()), _stream(q4)))
+    _lib.check(_entry, getattr(lib, _entry)(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()),
+                                            ctypes.c_size_t(ws.numel()), _stream(q4)))
   return out.view(q.shape) if q.dim() == 2 else out
+
+
+def ea_fwd(q, k, v, out_dtype=None):
+  """EA (bench/ea.mlir:13-17): out = softmax_features(q) (softmax_seq(k)^T v), [B,S,H,128]."""
+  return sima_fwd(q, k, v, out_dtype, _entry="asuka_b200_ea_fwd")
 
 
 def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None, tau=1.0, seed=0,

@@ -166,6 +166,13 @@ int asuka_b200_sima_workspace_bytes(const asuka_sima_params* p, size_t* bytes);
 int asuka_b200_sima_fwd(const asuka_sima_params* p, void* workspace, size_t workspace_bytes,
                         asuka_stream stream);
 
+/* ---- EA attention: replaces the generated kernels for bench/ea.mlir:13-17,
+ *      out = softmax(q over the 128 features) . (softmax(k over the sequence)^T . v) per (batch,
+ *      head).  Same tensors, same workspace size (asuka_b200_sima_workspace_bytes) and same
+ *      three-kernel streaming structure as SimA, plus a column-maximum pass over k. ---- */
+int asuka_b200_ea_fwd(const asuka_sima_params* p, void* workspace, size_t workspace_bytes,
+                      asuka_stream stream);
+
 /* ---- fused cases: forward + column scores (+ selection) enqueued back to back on one stream.
  *      `workspace` holds the row statistic between the two kernels: B*H*Sq floats. ---- */
 typedef struct {

@@ -142,7 +142,7 @@ def test_flop_conventions():
 def test_builder_interface():
   assert issubclass(B200Builder, Builder)
   with pytest.raises(ValueError):
-    B200Builder("EA")
+    B200Builder("Performer")
   f = B200Builder("H2O").build_callable()
   with pytest.raises(RuntimeError):
     f(torch.zeros(1), torch.zeros(1))                     # wrong arity

@@ -183,6 +183,29 @@ def test_sima_vs_oracle(ops, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 128, 1), (2, 1000, 3), (1, 4096, 4), (3, 2500, 2)])
+def test_ea_vs_oracle(ops, shape, dtype):
+  # bench/ea.mlir:13-17: softmax over the features of q, softmax over the sequence of k
+  import flashtensor_b200 as ft
+  B, S, H = shape
+  g = torch.Generator().manual_seed(S + H)
+  q = (2 * torch.randn(B, S, H, 128, generator=g)).to(dtype)
+  k = (2 * torch.randn(B, S, H, 128, generator=g)).to(dtype)
+  v = torch.randn(B, S, H, 128, generator=g).to(dtype)
+  ref = O.ea(q, k, v)
+  out16 = ft.EA(head_num=H, kv_head_num=H)(q.cuda(), k.cuda(), v.cuda())
+  out32 = ops.ea_fwd(q.cuda(), k.cuda(), v.cuda(), out_dtype=torch.float32)
+  torch.cuda.synchronize()
+  close(out32, ref, "ea f32 out")
+  close(out16, ref, "ea 16-bit out")
+  # a sequence-axis softmax that is dominated by one late key: exercises the column maximum
+  k2 = k.clone()
+  k2[:, S - 1] += 6
+  close(ops.ea_fwd(q.cuda(), k2.cuda(), v.cuda(), out_dtype=torch.float32), O.ea(q, k2, v), "ea peaked k")
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("direction", [1.0, -1.0])
 def test_logits_that_keep_growing_or_shrinking(ops, dtype, direction):
   # keys scaled by a ramp along the sequence: the running maximum of a row keeps moving (or the
