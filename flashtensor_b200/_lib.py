@@ -48,6 +48,10 @@ class SimaParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor)]
 
 
+class LinAttn32Params(ctypes.Structure):
+  _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor), ("ea", ctypes.c_int32)]
+
+
 class GatherParams(ctypes.Structure):
   _fields_ = [("k", Tensor), ("v", Tensor), ("idx", Tensor), ("k_out", Tensor), ("v_out", Tensor)]
 
@@ -80,6 +84,7 @@ SYMBOLS = {
     "asuka_b200_sima_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_sima_fwd": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_ea_fwd": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "asuka_b200_linattn32_fwd": (ctypes.c_int, [ctypes.POINTER(LinAttn32Params), ctypes.c_void_p]),
     "asuka_b200_case_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_h2o": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_h2o_static": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.c_void_p]),

@@ -13,7 +13,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libasuka_b200.so")
 
-SOURCES = ["capi.cu", "attn_fwd.cu", "col_scores.cu", "select_topk.cu", "score_ops.cu", "sima.cu"]
+SOURCES = ["capi.cu", "attn_fwd.cu", "col_scores.cu", "select_topk.cu", "score_ops.cu", "sima.cu", "linattn32.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v",

@@ -604,6 +604,39 @@ int asuka_b200_pool_scores(const asuka_tensor* score, const asuka_tensor* out, i
                                      kernel_size, static_cast<cudaStream_t>(stream)));
 }
 
+int asuka_b200_linattn32_fwd(const asuka_linattn32_params* p, asuka_stream stream) {
+  if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
+  const asuka_tensor* ts[4] = {&p->q, &p->k, &p->v, &p->out};
+  for (int i = 0; i < 4; ++i) {
+    const asuka_tensor& t = *ts[i];
+    if (t.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
+    if (t.dtype != ASUKA_F32) return ASUKA_ERR_BAD_DTYPE;
+    if (t.ndim != 4 || t.shape[3] != 32) return ASUKA_ERR_BAD_SHAPE;
+    for (int d = 0; d < 4; ++d)
+      if (t.shape[d] <= 0 || t.shape[d] != p->q.shape[d]) return ASUKA_ERR_BAD_SHAPE;
+    if (t.stride[3] != 1) return ASUKA_ERR_BAD_STRIDE;
+    for (int d = 0; d < 3; ++d)
+      if (t.stride[d] <= 0 || (t.stride[d] % 4) != 0) return ASUKA_ERR_BAD_STRIDE;
+    if ((reinterpret_cast<uintptr_t>(t.ptr) & 15u) != 0) return ASUKA_ERR_MISALIGNED;
+  }
+  if (p->ea != 0 && p->ea != 1) return ASUKA_ERR_BAD_ARGUMENT;
+  if (p->q.shape[0] * p->q.shape[2] > (1 << 24) || p->q.shape[1] > (1 << 24)) return ASUKA_ERR_TOO_LARGE;
+  int r;
+  if ((r = check_arch()) != ASUKA_OK) return r;
+  LinAttn32Args a;
+  a.q = static_cast<const float*>(p->q.ptr);
+  a.k = static_cast<const float*>(p->k.ptr);
+  a.v = static_cast<const float*>(p->v.ptr);
+  a.out = static_cast<float*>(p->out.ptr);
+  a.B = static_cast<int>(p->q.shape[0]); a.N = static_cast<int>(p->q.shape[1]); a.H = static_cast<int>(p->q.shape[2]);
+  a.ea = p->ea;
+  a.q_sb = p->q.stride[0]; a.q_sn = p->q.stride[1]; a.q_sh = p->q.stride[2];
+  a.k_sb = p->k.stride[0]; a.k_sn = p->k.stride[1]; a.k_sh = p->k.stride[2];
+  a.v_sb = p->v.stride[0]; a.v_sn = p->v.stride[1]; a.v_sh = p->v.stride[2];
+  a.o_sb = p->out.stride[0]; a.o_sn = p->out.stride[1]; a.o_sh = p->out.stride[2];
+  return map_cuda(launch_linattn32(a, static_cast<cudaStream_t>(stream)));
+}
+
 int asuka_b200_gather_kv(const asuka_gather_params* p, asuka_stream stream) {
   if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
   if (!is_16bit(p->k.dtype)) return p->k.ptr == nullptr ? ASUKA_ERR_NULL_POINTER : ASUKA_ERR_BAD_DTYPE;

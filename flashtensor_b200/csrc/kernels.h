@@ -74,6 +74,19 @@ struct GatherArgs {
 };
 cudaError_t launch_gather_kv(const GatherArgs& a, cudaStream_t stream);
 
+// linear attention at head_dim 32, f32: q, k, v, out [B, N, H, 32], strides in elements (unit stride
+// along the features, the others multiples of 4)
+struct LinAttn32Args {
+  const float* q;
+  const float* k;
+  const float* v;
+  float* out;
+  int B, N, H;
+  int ea;  // 1: EA (softmax normalisations), 0: SimA (L1 normalisations)
+  int64_t q_sb, q_sn, q_sh, k_sb, k_sn, k_sh, v_sb, v_sn, v_sh, o_sb, o_sn, o_sh;
+};
+cudaError_t launch_linattn32(const LinAttn32Args& a, cudaStream_t stream);
+
 struct SimaShape {
   int B, H, S;
   bool bf16;

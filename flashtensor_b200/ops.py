@@ -182,6 +182,19 @@ def ea_fwd(q, k, v, out_dtype=None):
   return sima_fwd(q, k, v, out_dtype, _entry="asuka_b200_ea_fwd")
 
 
+def linattn32_fwd(q, k, v, ea=False, out=None):
+  """SimA (ea=False) or EA (ea=True) attention core at head_dim 32 in f32 (bench/sima.mlir:13-17,
+  bench/ea.mlir:13-17).  q, k, v: [B, N, H, 32] f32, possibly strided views of a fused QKV tensor."""
+  lib = _lib.load()
+  _same_device(q, k, v, out)
+  with _on(q.device):
+    if out is None:
+      out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    p = _lib.LinAttn32Params(_desc(q), _desc(k), _desc(v), _desc(out), int(bool(ea)))
+    _lib.check("asuka_b200_linattn32_fwd", lib.asuka_b200_linattn32_fwd(ctypes.byref(p), _stream(q)))
+  return out
+
+
 def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None, tau=1.0, seed=0,
           k_keep=0, recent=0, n_idx=0, workspace=None, out=None, score=None, score_sq=None, idx=None):
   lib = _lib.load()

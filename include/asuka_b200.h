@@ -173,6 +173,20 @@ int asuka_b200_sima_fwd(const asuka_sima_params* p, void* workspace, size_t work
 int asuka_b200_ea_fwd(const asuka_sima_params* p, void* workspace, size_t workspace_bytes,
                       asuka_stream stream);
 
+/* ---- SimA / EA attention core at the reference's own benchmark shapes (bench/sima.mlir:13-17,
+ *      bench/ea.mlir:13-17: 64 x 4 heads x 784 x 32, f32): head_dim 32, f32 in and out.  q, k, v
+ *      may be strided views of the fused QKV projection's output (the asuka.split + reshape +
+ *      transpose of lines 6-12 then cost nothing); out [B, N, H, 32] is what lines 15-16 reshape
+ *      into the output projection's input.  HBM-bound: plain CUDA-core kernel, no workspace. ---- */
+typedef struct {
+  asuka_tensor q;   /* [B, N, H, 32] f32, unit stride along the last axis, others multiples of 4 */
+  asuka_tensor k;
+  asuka_tensor v;
+  asuka_tensor out; /* [B, N, H, 32] f32 */
+  int32_t ea;       /* 0: SimA (L1 normalisation over the sequence), 1: EA (softmax normalisations) */
+} asuka_linattn32_params;
+int asuka_b200_linattn32_fwd(const asuka_linattn32_params* p, asuka_stream stream);
+
 /* ---- fused cases: forward + column scores (+ selection) enqueued back to back on one stream.
  *      `workspace` holds the row statistic between the two kernels: B*H*Sq floats. ---- */
 typedef struct {

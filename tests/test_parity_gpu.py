@@ -205,6 +205,38 @@ def test_ea_vs_oracle(ops, shape, dtype):
   no_timeouts(ops)
 
 
+@pytest.mark.parametrize("ea", [False, True])
+def test_linear_attention_blocks_at_the_reference_bench_shapes(ops, ea):
+  # bench/sima.mlir / bench/ea.mlir: x [B, 784, 128] f32, 4 heads of 32; B reduced from 64 for the CPU oracle
+  from flashtensor_b200.blocks import EABlock, SimABlock
+  for (B, N, C) in [(3, 784, 128), (2, 100, 64), (1, 33, 32)]:
+    g = torch.Generator().manual_seed(N + C)
+    x = torch.randn(B, N, C, generator=g)
+    w_qkv = torch.randn(3 * C, C, generator=g) / C ** 0.5
+    b_qkv = torch.randn(3 * C, generator=g) * 0.1
+    w_o = torch.randn(C, C, generator=g) / C ** 0.5
+    b_o = torch.randn(C, generator=g) * 0.1
+    ref = O.linear_attention_block(x, w_qkv, b_qkv, w_o, b_o, ea)
+    block = EABlock() if ea else SimABlock()
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+      got = block(*(t.cuda() for t in (x, w_qkv, b_qkv, w_o, b_o)))
+    finally:
+      torch.backends.cuda.matmul.allow_tf32 = prev
+    e = O.errors(got, ref)
+    assert e["scale_rel"] <= 1e-4, e
+    # the core alone, on strided views, against the same line-by-line restatement without projections
+    q = torch.randn(B, N, 3, C // 32, 32, generator=g)
+    ref_core = O.linear_attention_core(q[:, :, 0], q[:, :, 1], q[:, :, 2], ea)
+    qd = q.cuda()
+    core = ops.linattn32_fwd(qd[:, :, 0], qd[:, :, 1], qd[:, :, 2], ea=ea)
+    e = O.errors(core, ref_core)
+    assert e["scale_rel"] <= 2e-5, e
+    assert torch.equal(core, ops.linattn32_fwd(qd[:, :, 0], qd[:, :, 1], qd[:, :, 2], ea=ea))
+  no_timeouts(ops)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("direction", [1.0, -1.0])
 def test_logits_that_keep_growing_or_shrinking(ops, dtype, direction):
