@@ -54,7 +54,7 @@ STREAMING = ("sima", "ea")   # HBM-bound two-pass programs: no S x S product
 
 # DRAM bytes per launch of the attention-forward kernel at the H2O workload, from the ncu capture
 # summarised in profiles/attn_fwd_h2o_c2.md (dram__bytes_read.sum + dram__bytes_write.sum).
-FWD_DRAM_TRAFFIC_BYTES = 161904640
+FWD_DRAM_TRAFFIC_BYTES = 160818944
 
 
 E2E_DEPTH = 2
