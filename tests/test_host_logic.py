@@ -95,6 +95,42 @@ def test_select_and_case_validation_codes(built_lib):
   assert lib.asuka_b200_sima_workspace_bytes(ctypes.byref(sp), ctypes.byref(need)) == -3
 
 
+def test_sibling_entry_points_validation_codes(built_lib):
+  # every check below fails before anything is launched (no GPU needed)
+  lib = _lib.load()
+  f32 = lambda shape, **kw: _t(shape, dtype=_lib.F32, **kw)
+  # score pooling: odd kernel size, distinct buffers
+  s3 = f32((1, 2, 512))
+  assert lib.asuka_b200_pool_scores(ctypes.byref(s3), ctypes.byref(f32((1, 2, 512), ptr=0x200000)), 4, None) == -10
+  assert lib.asuka_b200_pool_scores(ctypes.byref(s3), ctypes.byref(s3), 5, None) == -10
+  assert lib.asuka_b200_pool_scores(ctypes.byref(s3), ctypes.byref(f32((1, 2, 500), ptr=0x200000)), 5, None) == -3
+  # cache compaction: index tensor must be [B, H, n] i32 and the outputs [B, n, H, 128]
+  kv = _t((1, 256, 2, 128))
+  gp = lambda **kw: lib.asuka_b200_gather_kv(ctypes.byref(_lib.GatherParams(
+      kv, kv, kw.get("idx", _t((1, 2, 64), dtype=_lib.I32)), kw.get("ko", _t((1, 64, 2, 128), ptr=0x300000)),
+      kw.get("vo", _t((1, 64, 2, 128), ptr=0x400000)))), None)
+  assert gp(idx=_t((1, 3, 64), dtype=_lib.I32)) == -3
+  assert gp(idx=_t((1, 2, 64), dtype=_lib.F32)) == -2
+  assert gp(ko=_t((1, 32, 2, 128), ptr=0x300000)) == -3
+  # linear attention at head_dim 32: f32 only, last axis 32, 16-byte aligned
+  t32 = f32((2, 100, 4, 32))
+  la = lambda **kw: lib.asuka_b200_linattn32_fwd(ctypes.byref(_lib.LinAttn32Params(
+      kw.get("q", t32), kw.get("k", t32), kw.get("v", t32), kw.get("out", f32((2, 100, 4, 32), ptr=0x500000)),
+      kw.get("ea", 0))), None)
+  assert la(q=_t((2, 100, 4, 32))) == -2                       # 16-bit input
+  assert la(k=f32((2, 100, 4, 64))) == -3
+  assert la(v=f32((2, 100, 4, 32), ptr=0x1004)) == -5
+  assert la(out=f32((2, 100, 4, 32), strides=(12800, 128, 32, 2), ptr=0x500000)) == -4
+  assert la(ea=2) == -10
+  # EA shares SimA's checks
+  shp = (1, 256, 2, 128)
+  sp = _lib.SimaParams(_t(shp), _t(shp), _t(shp), _t(shp, dtype=_lib.I32))
+  assert lib.asuka_b200_ea_fwd(ctypes.byref(sp), ctypes.c_void_p(0x1000), 1 << 30, None) in (-2, -5, -3)
+  sp = _lib.SimaParams(_t(shp), _t(shp), _t(shp), _t(shp, ptr=0x600000))
+  assert lib.asuka_b200_ea_fwd(ctypes.byref(sp), ctypes.c_void_p(0x1000), 16, None) == -6
+  assert lib.asuka_b200_ea_fwd(ctypes.byref(sp), None, 1 << 30, None) == -1
+
+
 def test_ops_refuse_cpu_tensors(built_lib):
   from flashtensor_b200 import ops
   q = torch.zeros(1, 128, 1, 128, dtype=torch.float16)
