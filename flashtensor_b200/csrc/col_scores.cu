@@ -337,9 +337,19 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                                                        static_cast<uint32_t>(key), head_key);
                   x = fmaf(s[cc], scale, fmaf(l2, -p.inv_tau, -lv[e]));
                 } else {
-                  x = fmaf(s[cc], scale, -lv[e]);
+                  x = 0.f;  // (modes 0, 1, 4 take the packed path below)
                 }
-                s[cc] = ex2(x);
+                if constexpr (kMode == 2 || kMode == 3) s[cc] = ex2(x);
+              }
+              if constexpr (kMode != 2 && kMode != 3) {
+                // two logits per FMA instruction (packed f32x2 of sm_100)
+                const float2 sc2 = make_float2(scale, scale);
+                const float2 x01 = __ffma2_rn(make_float2(s[g * 4 + 0], s[g * 4 + 1]), sc2, make_float2(-lv[0], -lv[1]));
+                const float2 x23 = __ffma2_rn(make_float2(s[g * 4 + 2], s[g * 4 + 3]), sc2, make_float2(-lv[2], -lv[3]));
+                s[g * 4 + 0] = ex2(x01.x);
+                s[g * 4 + 1] = ex2(x01.y);
+                s[g * 4 + 2] = ex2(x23.x);
+                s[g * 4 + 3] = ex2(x23.y);
               }
             }
             if (tile_has_mask) {
@@ -350,11 +360,20 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
               for (int cc = 0; cc < 32; ++cc) hit = hit || (s[cc] >= noise[cc] && q_base + ch * 32 + cc < p.Sq);
             } else {
+              float2 a01 = make_float2(acc[0], acc[1]), a23 = make_float2(acc[2], acc[3]);
+              float2 q01 = make_float2(acc2[0], acc2[1]), q23 = make_float2(acc2[2], acc2[3]);
 #pragma unroll
-              for (int cc = 0; cc < 32; ++cc) {
-                acc[cc & 3] += s[cc];
-                if constexpr (kMode == 1) acc2[cc & 3] = fmaf(s[cc], s[cc], acc2[cc & 3]);
+              for (int cc = 0; cc < 32; cc += 4) {
+                const float2 p01 = make_float2(s[cc], s[cc + 1]), p23 = make_float2(s[cc + 2], s[cc + 3]);
+                a01 = __fadd2_rn(a01, p01);
+                a23 = __fadd2_rn(a23, p23);
+                if constexpr (kMode == 1) {
+                  q01 = __ffma2_rn(p01, p01, q01);
+                  q23 = __ffma2_rn(p23, p23, q23);
+                }
               }
+              acc[0] = a01.x; acc[1] = a01.y; acc[2] = a23.x; acc[3] = a23.y;
+              acc2[0] = q01.x; acc2[1] = q01.y; acc2[2] = q23.x; acc2[3] = q23.y;
             }
           }
         } else {
