@@ -406,7 +406,7 @@ def main():
     dt1, _ = cpu_oracle_sample(args.case, w, 1, threads)             # warm-up and size estimate
     heads = max(1, min(w["H"], int(4.0 / max(dt1, 1e-3))))            # ~4 s per pass
     passes, spent, fl_total = 0, 0.0, 0
-    while spent < 12.0 and passes < 8:                                # ~12-20 s of CPU work in all
+    while spent < 12.0 and passes < 64:                               # ~12-20 s of CPU work in all
       dt, fl = cpu_oracle_sample(args.case, w, heads, threads)
       spent += dt
       fl_total += fl
