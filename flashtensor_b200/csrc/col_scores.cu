@@ -424,7 +424,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // thread walking its own row in global memory wastes most of every sector.  The plain variant
 // (direct loads) serves noise tensors whose strides TMA cannot describe.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRsThreads = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 rows
+constexpr int kRsThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 rows (two per 32 rows: columns 0..63 / 64..127)
 constexpr uint32_t kNoiseTileBytes = 128 * 128 * 4;
 template <int kNoise> struct RsCfg {  // kNoise 1: the noise tile shares the stage with K
   static constexpr bool kNoiseTma = kNoise == 1;
@@ -473,11 +473,11 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     for (int i = 0; i < kStages; ++i) {
       mbar_init(smem_u32(&bars.k_full[i]), 1);
       // the MMA commit, plus (TMA variant) one arrival per row warp once the noise has been read
-      mbar_init(smem_u32(&bars.k_empty[i]), kNoiseTma ? 5 : 1);
+      mbar_init(smem_u32(&bars.k_empty[i]), kNoiseTma ? 9 : 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars.s_full[i]), 1);
-      mbar_init(smem_u32(&bars.s_empty[i]), 128);
+      mbar_init(smem_u32(&bars.s_empty[i]), 256);
     }
     mbar_fence_init();
   }
@@ -553,7 +553,11 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
     }
   } else {
-    const int wq = warp & 3;  // warps 2,3,4,5 -> lane quarters 2,3,0,1
+    // Two warps per 32 rows, each with half of every tile's columns and its own running (maximum,
+    // sum): a row's statistic is a plain merge of the two at the end, so nothing is exchanged per
+    // step, and the scheduler gets twice the warps to hide the noise generator's ALU latency.
+    const int wq = warp & 3;           // TMEM lane quarter (warps 2..9 -> 2,3,0,1,2,3,0,1)
+    const int half = (warp - 2) >> 2;  // columns 0..63 or 64..127 of every tile
     const int r_in_tile = wq * 32 + lane;
     const int row = q0 + r_in_tile;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
@@ -576,7 +580,7 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const int thr = lim - j * kTile;  // columns > thr are masked
       const uint8_t* noise_tile = smem_gen + kTileBytes + st * Cfg::kStageBytes + kTileBytes;
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
+      for (int c4 = half * 2; c4 < half * 2 + 2; ++c4) {
         uint32_t u[32];
         tmem_ld32(tbase + lane_base + buf * 128 + c4 * 32, u);
         float er[32];
@@ -624,7 +628,12 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (lane == 0) mbar_arrive(smem_u32(&bars.k_empty[st]));
       }
     }
-    if (ok && row < p.Sq) lse_out[(static_cast<size_t>(b) * p.H + h) * p.Sq + row] = m + log2f(l);
+    // hand-over through the Q tile's shared memory: every MMA that read it has retired (this thread
+    // has seen the last S tile), and the variant with the staged noise has no other room left
+    float* part = reinterpret_cast<float*>(smem_gen);  // [m, l][half][row]
+    part[(0 * 2 + half) * kTile + r_in_tile] = m;
+    part[(1 * 2 + half) * kTile + r_in_tile] = l;
+    if (!ok) *abortp = 1u;
   }
 
   tc_fence_before_sync();
@@ -632,6 +641,20 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tbase, 256);
+  }
+  if (warp >= 2 && warp < 6 && !*abortp) {
+    // merge the two halves of every row (in column order)
+    const int r_in_tile = (warp & 3) * 32 + lane;
+    const int row = q0 + r_in_tile;
+    const float* part = reinterpret_cast<const float*>(smem_gen);
+    const float m0 = part[0 * kTile + r_in_tile], m1 = part[1 * kTile + r_in_tile];
+    const float m = fmaxf(m0, m1);
+    if (row < p.Sq) {
+      // (a half with no visible column has sum 0 and maximum -inf: give it weight 0, not NaN)
+      const float l = part[2 * kTile + r_in_tile] * (m0 > -INFINITY ? ex2(m0 - m) : 0.f) +
+                      part[3 * kTile + r_in_tile] * (m1 > -INFINITY ? ex2(m1 - m) : 0.f);
+      lse_out[(static_cast<size_t>(b) * p.H + h) * p.Sq + row] = m + log2f(l);
+    }
   }
 }
 
