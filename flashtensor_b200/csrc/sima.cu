@@ -64,8 +64,8 @@ struct StatsParams {
 };
 
 struct StBars {
-  uint64_t full[kStStages], empty[kStStages], m_done;
-  uint64_t ktrans[kStStages];  // EA only: the K tile of the stage has been exponentiated in place
+  uint64_t full[3], empty[3], m_done;  // (two stages in SimA mode, three in EA mode)
+  uint64_t ktrans[3];                  // EA only: the K tile of the stage has been exponentiated in place
 };
 
 template <bool kBF16>
@@ -171,6 +171,10 @@ template <bool kBF16, bool kEA>
 __global__ void __launch_bounds__(kStThreads, 1)
 sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const StatsParams p) {
+  // EA does not read Q in this pass: the same shared memory then holds three stages of [K | V]
+  // instead of two of [K | V | Q], i.e. two stages instead of one in flight while one is consumed
+  constexpr int kSt = kEA ? 3 : 2;
+  constexpr uint32_t kStageBytes = (kEA ? 2 : 3) * kTileBytes;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) StBars bars;
   __shared__ float red[2][8][kTile];
@@ -190,12 +194,12 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   if (tid == 0) {
     abort_s = 0;
-    for (int i = 0; i < kStStages; ++i) {
+    for (int i = 0; i < kSt; ++i) {
       mbar_init(smem_u32(&bars.full[i]), 1);
       mbar_init(smem_u32(&bars.empty[i]), 1 + 8);
     }
     mbar_init(smem_u32(&bars.m_done), 1);
-    for (int i = 0; i < kStStages; ++i) mbar_init(smem_u32(&bars.ktrans[i]), 256);
+    for (int i = 0; i < kSt; ++i) mbar_init(smem_u32(&bars.ktrans[i]), 256);
     mbar_fence_init();
   }
   if constexpr (kEA) {
@@ -221,14 +225,14 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (warp == 0) {
     if (lane == 0) {
       for (int i = 0; i < ntile; ++i) {
-        const int st = i % kStStages;
-        const uint32_t use = static_cast<uint32_t>(i / kStStages);
+        const int st = i % kSt;
+        const uint32_t use = static_cast<uint32_t>(i / kSt);
         if (use > 0 && !mbar_wait(smem_u32(&bars.empty[st]), (use - 1) & 1, abortp)) {
           record_timeout(p.status, 41);
           break;
         }
         const uint32_t bar = smem_u32(&bars.full[st]);
-        const uint32_t base = smem_base + st * 3 * kTileBytes;
+        const uint32_t base = smem_base + st * kStageBytes;
         const int s0 = (tile0 + i) * kTile;
         mbar_expect_tx(bar, (kEA ? 2 : 3) * kTileBytes);
         tma_load_4d(base, &map_k, bar, 0, h, s0, b);
@@ -248,15 +252,15 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_MN_MAJOR, UMMA_MN_MAJOR, 128, 128);
       bool ok = true;
       for (int i = 0; i < ntile && ok; ++i) {
-        const int st = i % kStStages;
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp));
+        const int st = i % kSt;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kSt) & 1, abortp));
         if (!ok) { if (lane == 0) record_timeout(p.status, 42); break; }
         if constexpr (kEA) {
-          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.ktrans[st]), (i / kStStages) & 1, abortp));
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.ktrans[st]), (i / kSt) & 1, abortp));
           if (!ok) { if (lane == 0) record_timeout(p.status, 45); break; }
         }
         tc_fence_after_sync();
-        const uint32_t base = smem_base + st * 3 * kTileBytes;
+        const uint32_t base = smem_base + st * kStageBytes;
         // M = K^T V: TMEM lane = d, column = e
         const uint64_t adesc = umma_smem_desc_sw128(base, kHalfBytes, 1024);               // K
         const uint64_t bdesc = umma_smem_desc_sw128(base + kTileBytes, kHalfBytes, 1024);  // V
@@ -282,13 +286,13 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     bool ok = true;
     for (int i = 0; i < ntile; ++i) {
-      const int st = i % kStStages;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kStStages) & 1, abortp));
+      const int st = i % kSt;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kSt) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 43); break; }
       if constexpr (kEA) {
         // all 256 threads work on the K tile: rows 16 apart per thread; k' = exp(k - colmax),
         // rounded to the input type and written back for the MMA; rows past the sequence give 0
-        uint8_t* tile = smem_gen + st * 3 * kTileBytes + (chunk16 >> 3) * kHalfBytes;
+        uint8_t* tile = smem_gen + st * kStageBytes + (chunk16 >> 3) * kHalfBytes;
         const int rg16 = which * 8 + rg;
         const int s0 = (tile0 + i) * kTile;
         float cm[8];
@@ -310,7 +314,7 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         fence_proxy_async_smem();  // written by ordinary stores, read by the tensor pipe
         mbar_arrive(smem_u32(&bars.ktrans[st]));
       } else {
-        const uint8_t* tile = smem_gen + st * 3 * kTileBytes + (which ? 2 * kTileBytes : 0) +
+        const uint8_t* tile = smem_gen + st * kStageBytes + (which ? 2 * kTileBytes : 0) +
                               (chunk16 >> 3) * kHalfBytes;
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
@@ -450,8 +454,7 @@ __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p
 // 3. out = (Q M'') * inv_scale
 // ---------------------------------------------------------------------------------------------
 constexpr int kOutThreads = 256;  // warp 0 producer, warp 1 MMA, warps 4-7 epilogue
-constexpr int kOutStages = 3;
-constexpr uint32_t kOutSmem = (1 + kOutStages + 2) * kTileBytes + 1024;
+constexpr uint32_t kOutSmem = (1 + 4 + 2) * kTileBytes + 1024;  // M'', up to four Q stages, two staging buffers
 
 struct OutParams {
   int B, H, S;
@@ -463,8 +466,8 @@ struct OutParams {
 };
 
 struct OutBars {
-  uint64_t m_full, q_full[kOutStages], q_empty[kOutStages], acc_full[2], acc_empty[2];
-  uint64_t qtrans[kOutStages];  // EA only: the Q tile of the stage has been exponentiated in place
+  uint64_t m_full, q_full[4], q_empty[4], acc_full[2], acc_empty[2];
+  uint64_t qtrans[4];  // EA only: the Q tile of the stage has been exponentiated in place
 };
 
 // kEA: softmax over the features of every query row (bench/ea.mlir:13): the row's thread
@@ -474,16 +477,18 @@ template <bool kBF16, bool kOutF32, bool kEA>
 __global__ void __launch_bounds__(kOutThreads + (kEA ? 256 : 0), 1)  // EA: warps 8-15 exponentiate Q
 sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_m,
                 const __grid_constant__ CUtensorMap map_o, const OutParams p) {
+  // four Q stages (three in flight) where shared memory allows it; EA's extra state leaves room for three
+  constexpr int kQ = kEA ? 3 : 4;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) OutBars bars;
-  __shared__ float inv_r_s[kOutStages + 2][kTile];  // EA: 1 / row sum of the exponentiated Q rows, ring over tiles
+  __shared__ float inv_r_s[kEA ? kQ + 2 : 1][kTile];  // EA: 1 / row sum of the exponentiated Q rows, ring over tiles
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sM = smem_base;
   const uint32_t sQ = smem_base + kTileBytes;
-  const uint32_t sO = sQ + kOutStages * kTileBytes;  // two 32 KB staging buffers (one 64 KB for f32)
+  const uint32_t sO = sQ + kQ * kTileBytes;  // two 32 KB staging buffers (one 64 KB for f32)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile uint32_t* abortp = &abort_s;
@@ -496,7 +501,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (tid == 0) {
     abort_s = 0;
     mbar_init(smem_u32(&bars.m_full), 1);
-    for (int i = 0; i < kOutStages; ++i) {
+    for (int i = 0; i < kQ; ++i) {
       mbar_init(smem_u32(&bars.q_full[i]), 1);
       mbar_init(smem_u32(&bars.q_empty[i]), 1);
     }
@@ -504,7 +509,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(smem_u32(&bars.acc_full[i]), 1);
       mbar_init(smem_u32(&bars.acc_empty[i]), 128);
     }
-    for (int i = 0; i < kOutStages; ++i) mbar_init(smem_u32(&bars.qtrans[i]), 256);
+    for (int i = 0; i < kQ; ++i) mbar_init(smem_u32(&bars.qtrans[i]), 256);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -526,8 +531,8 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tma_load_4d(sM + kHalfBytes, &map_m, bar, 64, 0, bh * kTile, 0);
       }
       for (int i = 0; i < ntile; ++i) {
-        const int st = i % kOutStages;
-        const uint32_t use = static_cast<uint32_t>(i / kOutStages);
+        const int st = i % kQ;
+        const uint32_t use = static_cast<uint32_t>(i / kQ);
         if (use > 0 && !mbar_wait(smem_u32(&bars.q_empty[st]), (use - 1) & 1, abortp)) {
           record_timeout(p.status, 51);
           break;
@@ -550,11 +555,11 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       bool ok = wait_all(&bars.m_full, 0, 52);
       const uint64_t mdesc = umma_smem_desc_sw128(sM, 16, 1024);
       for (int i = 0; i < ntile && ok; ++i) {
-        const int st = i % kOutStages, buf = i & 1;
-        ok = wait_all(&bars.q_full[st], (i / kOutStages) & 1, 53);
+        const int st = i % kQ, buf = i & 1;
+        ok = wait_all(&bars.q_full[st], (i / kQ) & 1, 53);
         if (!ok) break;
         if constexpr (kEA) {
-          ok = wait_all(&bars.qtrans[st], (i / kOutStages) & 1, 56);
+          ok = wait_all(&bars.qtrans[st], (i / kQ) & 1, 56);
           if (!ok) break;
         }
         if (i >= 2) {
@@ -584,8 +589,8 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int r = t256 >> 1, half = t256 & 1;
     bool ok = true;
     for (int i = 0; i < ntile && ok; ++i) {
-      const int st = i % kOutStages;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_full[st]), (i / kOutStages) & 1, abortp));
+      const int st = i % kQ;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_full[st]), (i / kQ) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 57); break; }
       uint8_t* tile = smem_gen + (sQ - smem_base) + st * kTileBytes + half * kHalfBytes;
       uint4 raw[8];
@@ -615,7 +620,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // The slot last held tile i - 5.  This tile's Q landed only after the MMA of tile i - 3 had
       // retired, that MMA was issued only after the epilogue of tile i - 5 had released its
       // accumulator, and the epilogue reads its 1/sum before it does that.
-      if (half == 0) inv_r_s[i % (kOutStages + 2)][r] = 1.f / sum;
+      if (half == 0) inv_r_s[i % (kQ + 2)][r] = 1.f / sum;
       fence_proxy_async_smem();  // the tile was written by ordinary stores, the tensor pipe reads it
       mbar_arrive(smem_u32(&bars.qtrans[st]));
     }
@@ -633,7 +638,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_full[buf]), (i >> 1) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 55); break; }
       tc_fence_after_sync();
-      const float inv_r = kEA ? inv_r_s[i % (kOutStages + 2)][r] : 1.f;
+      const float inv_r = kEA ? inv_r_s[i % (kQ + 2)][r] : 1.f;
       // the staging buffer about to be overwritten must have been read by its previous store
       if constexpr (!kOutF32) {
         if (tid == 128) tma_store_wait_read_n<1>();
@@ -818,9 +823,10 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
       if (s.out_f32) kern = s.bf16 ? sima_out_kernel<true, true, false> : sima_out_kernel<false, true, false>;
       else kern = s.bf16 ? sima_out_kernel<true, false, false> : sima_out_kernel<false, false, false>;
     }
-    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kOutSmem);
+    const uint32_t out_smem = s.ea ? kOutSmem - kTileBytes : kOutSmem;  // EA runs three Q stages
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(out_smem));
     if (e != cudaSuccess) return e;
-    kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads + (s.ea ? 256 : 0), kOutSmem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);
+    kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads + (s.ea ? 256 : 0), out_smem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);
     count_launch();
     e = cudaPeekAtLastError();
   }
