@@ -7,8 +7,10 @@
 //                 n_j = q_len - max(0, j - (S - q_len)); larger mean first, then larger std, then
 //                 lower index
 // One CTA per row.  Keys are mapped to order-preserving unsigned integers and kept in shared
-// memory; an MSB-first radix select (8 bits per pass, warp-aggregated histogram updates) finds the
-// k-th largest key exactly, then an ordered block scan compacts the kept indices.  Everything is
+// memory; an MSB-first radix select (11 bits per pass: three passes for 32-bit keys, six for 64-bit
+// ones; shared-memory atomics on a 2048-bin histogram, warp-aggregated where equal digits are
+// common) finds the k-th largest key exactly, then an ordered block scan compacts the kept
+// indices.  Everything is
 // integer work on exact keys, so the result is deterministic.
 #include "../../include/asuka_b200.h"
 #include "kernels.h"
@@ -43,11 +45,15 @@ __device__ __forceinline__ uint64_t make_key<uint64_t>(const SelectArgs& a, cons
   return (static_cast<uint64_t>(mono_f32(mean)) << 32) | mono_f32(sd);
 }
 
+constexpr int kDigitBits = 11;
+constexpr int kBins = 1 << kDigitBits;  // two bins per thread
+
 template <typename KeyT>
 __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const SelectArgs a) {
   extern __shared__ __align__(16) uint8_t sel_smem[];
   KeyT* keys = reinterpret_cast<KeyT*>(sel_smem);
-  __shared__ uint32_t hist[256];
+  __shared__ uint32_t hist[kBins];
+  __shared__ uint32_t warp_sum[32];
   __shared__ unsigned long long warp_tot[32];
   __shared__ KeyT s_prefix;
   __shared__ uint32_t s_k;
@@ -61,13 +67,17 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const SelectArgs
   const int ncand = a.mode == ASUKA_SELECT_TOPK_RECENT ? a.S - a.recent : a.S;
 
   for (int j = tid; j < ncand; j += kSelThreads) keys[j] = make_key<KeyT>(a, srow, qrow, j);
+  hist[tid] = 0;
+  hist[tid + kSelThreads] = 0;
   __syncthreads();
 
+  constexpr int kKeyBits = static_cast<int>(sizeof(KeyT)) * 8;
   KeyT prefix = 0, mask = 0;
   uint32_t k = static_cast<uint32_t>(a.k_keep);
-  for (int shift = static_cast<int>(sizeof(KeyT)) * 8 - 8; shift >= 0; shift -= 8) {
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
+  for (int hi = kKeyBits; hi > 0; hi -= kDigitBits) {
+    // this pass looks at bits [lo, hi); the last pass of a key may be narrower than 11 bits
+    const int lo = hi > kDigitBits ? hi - kDigitBits : 0;
+    const uint32_t dmask = (1u << (hi - lo)) - 1u;
     for (int base = 0; base < ncand; base += kSelThreads) {
       const int j = base + tid;
       bool in = false;
@@ -75,45 +85,64 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const SelectArgs
       if (j < ncand) {
         const KeyT key = keys[j];
         in = (key & mask) == prefix;
-        digit = static_cast<uint32_t>(key >> shift) & 255u;
+        digit = static_cast<uint32_t>(key >> lo) & dmask;
       }
       const uint32_t act = __ballot_sync(0xffffffffu, in);
-      if (in) {
-        const uint32_t peers = __match_any_sync(act, digit);
-        if (lane == __ffs(peers) - 1) atomicAdd(&hist[digit], __popc(peers));
+      if (act == 0u) continue;
+      if constexpr (sizeof(KeyT) == 8) {
+        // composite (mean, std) keys share most of their leading bits: aggregate equal digits in
+        // the warp before touching the histogram
+        if (in) {
+          const uint32_t peers = __match_any_sync(act, digit);
+          if (lane == __ffs(peers) - 1) atomicAdd(&hist[digit], __popc(peers));
+        }
+      } else {
+        // scores spread over the bins, so plain atomics rarely collide; the one degenerate case
+        // worth a check is a warp whose live keys all carry the same digit
+        const int leader = __ffs(act) - 1;
+        const uint32_t d0 = __shfl_sync(0xffffffffu, digit, leader);
+        if (__all_sync(0xffffffffu, !in || digit == d0)) {
+          if (lane == leader) atomicAdd(&hist[d0], __popc(act));
+        } else if (in) {
+          atomicAdd(&hist[digit], 1u);
+        }
       }
     }
     __syncthreads();
-    if (warp == 0) {
-      uint32_t c[8], tot = 0;
+    // Find the digit d with count(digits > d) < k <= count(digits >= d).  Thread t owns bins 2t and
+    // 2t + 1; suffix sums run over the lanes of a warp, then over the 32 warps.
+    const uint32_t c0 = hist[2 * tid], c1 = hist[2 * tid + 1];
+    hist[2 * tid] = 0;      // (cleared for the next pass; nobody else reads these two bins)
+    hist[2 * tid + 1] = 0;
+    const uint32_t mine = c0 + c1;
+    uint32_t incl = mine;   // sum over lanes >= this one of this warp
 #pragma unroll
-      for (int d = 0; d < 8; ++d) {
-        c[d] = hist[lane * 8 + d];
-        tot += c[d];
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t v = __shfl_down_sync(0xffffffffu, incl, off);
+      if (lane + off < 32) incl += v;
+    }
+    if (lane == 0) warp_sum[warp] = incl;
+    __syncthreads();
+    uint32_t higher = 0;    // keys in the bins of all higher warps
+    {
+      const uint32_t v = (lane > warp) ? warp_sum[lane] : 0u;
+      higher = __reduce_add_sync(0xffffffffu, v);
+    }
+    const uint32_t above = higher + incl - mine;  // keys with a digit above this thread's two bins
+    if (above < k && k <= above + mine) {
+      uint32_t r = k - above;
+      int d = 2 * tid + 1;
+      if (c1 < r) {
+        r -= c1;
+        d = 2 * tid;
       }
-      uint32_t incl = tot;  // sum over lanes >= this one (higher digits)
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t v = __shfl_down_sync(0xffffffffu, incl, off);
-        if (lane + off < 32) incl += v;
-      }
-      const uint32_t above = incl - tot;
-      if (above < k && k <= incl) {
-        uint32_t r = k - above;
-        int dsel = 0;
-#pragma unroll
-        for (int d = 7; d >= 0; --d) {
-          if (c[d] >= r) { dsel = d; break; }
-          r -= c[d];
-        }
-        s_prefix = prefix | (static_cast<KeyT>(lane * 8 + dsel) << shift);
-        s_k = r;
-      }
+      s_prefix = prefix | (static_cast<KeyT>(d) << lo);
+      s_k = r;
     }
     __syncthreads();
     prefix = s_prefix;
     k = s_k;
-    mask |= static_cast<KeyT>(255) << shift;
+    mask |= static_cast<KeyT>(dmask) << lo;
   }
   // prefix is now the k-th largest key T; k of the keys equal to T are kept, lowest index first.
 
