@@ -4,8 +4,9 @@ Each class mirrors the eager module of the same name in the reference (``cases/k
 ``h2o.py``, ``kf.py``, ``roco.py``): same constructor arguments, same ``forward`` arguments and
 return order, same ``prepare`` dictionary, and a module-level ``get_model``-style factory.  The
 body of ``forward`` is the hand-written sm_100a kernel library instead of PyTorch eager or a
-generated Triton kernel.  ``SimA`` has no Python counterpart in the reference (only
-``bench/sima.mlir``); its signature follows the other cases.
+generated Triton kernel.  ``SimA`` and ``EA`` have no Python counterpart in the reference (only
+``bench/sima.mlir`` and ``bench/ea.mlir``); their signature follows the other cases.  The sibling
+cases ``Gemma2``, ``SnapKV`` and ``Corm`` mirror ``cases/kernels/{gemma2,snapkv,corm}.py``.
 
 The ``select`` methods are additions the benchmark configuration defines (the reference stops at
 the scores): they return the kept key indices as ascending int32.
