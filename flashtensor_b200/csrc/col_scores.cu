@@ -155,6 +155,18 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
+    // the K tiles are the first thing every role waits for: start them now, under the TMEM
+    // allocation and the CTA-wide barrier below (this thread initialised the barrier they signal)
+    {
+      const uint32_t bar = smem_u32(&bars.k_full);
+      mbar_expect_tx(bar, kTileBytes * n_active);
+      for (int t = 0; t < 2; ++t) {
+        if (active[t]) {
+          tma_load_4d(sK + t * kTileBytes, &map_k, bar, 0, h / p.group, kv0[t], b);
+          tma_load_4d(sK + t * kTileBytes + kHalfBytes, &map_k, bar, 64, h / p.group, kv0[t], b);
+        }
+      }
+    }
   }
   if (warp == 1) {
     __syncwarp();
@@ -168,16 +180,6 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (whole warp)
-    if (lane == 0) {
-      const uint32_t bar = smem_u32(&bars.k_full);
-      mbar_expect_tx(bar, kTileBytes * n_active);
-      for (int t = 0; t < 2; ++t) {
-        if (active[t]) {
-          tma_load_4d(sK + t * kTileBytes, &map_k, bar, 0, h / p.group, kv0[t], b);
-          tma_load_4d(sK + t * kTileBytes + kHalfBytes, &map_k, bar, 64, h / p.group, kv0[t], b);
-        }
-      }
-    }
     const float* lse_row = p.lse2 + (static_cast<size_t>(b) * p.H + h) * p.Sq;
     bool ok = true;
     for (int i = i_begin; i < p.nq_tiles; ++i) {
