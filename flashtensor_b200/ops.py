@@ -222,7 +222,10 @@ def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None,
       workspace = torch.empty((max(nbytes.value, 16),), dtype=torch.uint8, device=dev)
     _lib.check(fn_name, getattr(lib, fn_name)(ctypes.byref(p), ctypes.c_void_p(workspace.data_ptr()),
                                               ctypes.c_size_t(workspace.numel()), _stream(q4)))
-  out = out.view(q.shape) if q.dim() == 2 else out
+  if q.dim() == 2:
+    # the 2-D scripts return out [q_len, H*128] and per-key tensors [Hkv, kv_len] (cases/attn_h2o.py:47)
+    out = out.view(q.shape)
+    score, score_sq, idx = (None if t is None else t[0] for t in (score, score_sq, idx))
   return out, score, score_sq, idx
 
 

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN_NAMES, load_golden
+from conftest import GOLDEN_NAMES, GQA_GOLDEN_NAMES, load_golden
 from oracle import attn_oracle as O
 
 
@@ -39,6 +39,20 @@ def test_oracle_matches_reference_fixture(name):
       continue
     # same torch ops in the same order on the same host: differences are rounding noise only
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", GQA_GOLDEN_NAMES)
+def test_grouped_query_oracle_matches_reference_fixture(name):
+  # cases/attn_h2o.py AttnH2O / cases/attn.py Attn in their own 2-D layout, K/V heads < query heads
+  g = load_golden(name)
+  H, Hkv, causal = g["head_num"], g["kv_head_num"], bool(g["masked"])
+  q4 = g["q"].view(1, -1, H, 128)
+  k4, v4 = g["k"].view(1, -1, Hkv, 128), g["v"].view(1, -1, Hkv, 128)
+  out, score = O.h2o_gqa(q4, k4, v4, causal)
+  torch.testing.assert_close(out.reshape(q4.shape[1], H * 128), g["outs"][0], rtol=1e-5, atol=1e-6)
+  if len(g["outs"]) > 1:
+    assert g["outs"][1].shape == (Hkv, k4.shape[1])
+    torch.testing.assert_close(score[0], g["outs"][1], rtol=1e-5, atol=1e-6)
 
 
 def test_causal_mask_convention():

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN_NAMES, load_golden
+from conftest import GOLDEN_NAMES, GQA_GOLDEN_NAMES, load_golden
 from oracle import attn_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -74,6 +74,27 @@ def test_against_reference_fixture(ops, name):
       assert got.dtype == torch.bool and want.any() and not want.all()
       assert torch.all((margin[differ] - 1).abs() < 1e-3), f"{int(differ.sum())} decisions differ off the threshold"
       continue
+    close(got, want, f"{name} output {i}")
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("name", GQA_GOLDEN_NAMES)
+def test_grouped_query_against_reference_fixture(ops, name):
+  # fixtures from the reference's own AttnH2O / Attn modules (cases/attn_h2o.py:20-89,
+  # cases/attn.py:20-63) in their 2-D layout, K/V heads shared by groups of query heads
+  import flashtensor_b200 as ft
+  g = load_golden(name)
+  H, Hkv, causal = g["head_num"], g["kv_head_num"], bool(g["masked"])
+  q, k, v = g["q"].cuda(), g["k"].cuda(), g["v"].cuda()
+  assert q.dim() == 2 and q.shape[1] == H * 128 and k.shape[1] == Hkv * 128
+  if name.startswith("gqa_attn"):
+    outs = (ft.Attn(head_num=H, kv_head_num=Hkv, causal=causal)(q, k, v),)
+  else:
+    outs = ft.H2O(head_num=H, kv_head_num=Hkv, causal=causal)(q, k, v)
+  torch.cuda.synchronize()
+  assert len(outs) == len(g["outs"])
+  for i, (got, want) in enumerate(zip(outs, g["outs"])):
+    assert tuple(got.shape) == tuple(want.shape)
     close(got, want, f"{name} output {i}")
   no_timeouts(ops)
 
