@@ -131,6 +131,7 @@ def test_seeded_noise_generator():
   assert not np.array_equal(w[0, 0], w[0, 1])              # heads differ
   assert not np.array_equal(w, O.keyformer_seeded_bits(4, 1, 2, 64, 128))
   assert np.array_equal(w, O.keyformer_seeded_bits(3, 1, 2, 64, 128))
+  assert np.array_equal(O.keyformer_seeded_bits(3, 1, 2, 64, 128, units=[1])[0], w[0, 1])   # one unit alone
   er = O.keyformer_seeded_exp_rand(3, 2, 2, 256, 256)
   assert er.shape == (2, 2, 256, 256) and torch.all(er > 0) and torch.isfinite(er).all()
   g = -er.double().log()                                   # Gumbel(0,1): mean 0.5772, var pi^2/6

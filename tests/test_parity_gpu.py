@@ -564,3 +564,96 @@ def test_full_size_roco_and_sima_properties(ops):
   qn = q.float() / q.float().abs().sum(1, keepdim=True)
   torch.testing.assert_close(o1, qn.sum(-1, keepdim=True).expand_as(o1), rtol=0, atol=float(o1.abs().max()) * 2e-3)
   no_timeouts(ops)
+
+
+# ------------------------------------------------------------------------------------------
+# (4) the benchmark configurations at their own size: whole configuration on the GPU, a few
+#     (batch, head) units of it against the CPU oracle
+# ------------------------------------------------------------------------------------------
+def _gpu_inputs(B, S, H, dtype, seed, uniform_v=False):
+  g = torch.Generator(device="cuda").manual_seed(seed)
+  q = torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.float32).to(dtype)
+  k = torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.float32).to(dtype)
+  if uniform_v:
+    v = (torch.rand(B, S, H, 128, generator=g, device="cuda", dtype=torch.float32) * 2 - 1).to(dtype)
+  else:
+    v = torch.randn(B, S, H, 128, generator=g, device="cuda", dtype=torch.float32).to(dtype)
+  return q, k, v
+
+
+def _unit(t, b, h):
+  """[B,S,H,D] -> the (b, h) unit as a CPU tensor [1,S,1,D]."""
+  return t[b:b + 1, :, h:h + 1].cpu()
+
+
+def test_full_size_keyformer_units_vs_oracle(ops):
+  # configuration C3: fp16 B=4 H=32 S=2048, tau 1.5, top-k = S/4, both noise sources
+  import flashtensor_b200 as ft
+  B, S, H, tau, k_keep = 4, 2048, 32, 1.5, 512
+  q, k, v = _gpu_inputs(B, S, H, torch.float16, 3)
+  model = ft.KeyFormer(tau=tau, head_num=H, kv_head_num=H)
+  units = [(0, 0), (3, 17)]
+  # (a) the exp_rand operand of cases/kernels/kf.py:48
+  g = torch.Generator(device="cuda").manual_seed(33)
+  er = 1 + torch.randn(B, H, S, S, generator=g, device="cuda").abs()
+  out, score, idx = model.select(q, k, v, er, k_keep)
+  torch.cuda.synchronize()
+  for b, h in units:
+    ref_out, ref_score = O.keyformer(_unit(q, b, h), _unit(k, b, h), _unit(v, b, h), er[b:b + 1, h:h + 1].cpu(), tau)
+    close(out[b:b + 1, :, h:h + 1], ref_out, f"C3 operand unit ({b},{h}) out")
+    close(score[b:b + 1, h:h + 1], ref_score, f"C3 operand unit ({b},{h}) kf_score")
+    got_idx = idx[b:b + 1, h:h + 1].cpu().numpy()
+    assert np.array_equal(got_idx, O.keyformer_select(score[b:b + 1, h:h + 1].cpu().numpy(), k_keep))
+    O.check_index_sets(got_idx, O.keyformer_select(ref_score.numpy(), k_keep), ref_score.numpy(), k_keep)
+  del er
+  # (b) Gumbel noise generated in the kernels from a seed
+  seed = 2024
+  out2, score2, idx2 = model.seeded(q, k, v, seed, k_keep)
+  torch.cuda.synchronize()
+  assert torch.equal(out2, out)
+  for b, h in units:
+    er_u = O.keyformer_seeded_exp_rand(seed, B, H, S, S, units=[b * H + h])[None]
+    ref_out, ref_score = O.keyformer(_unit(q, b, h), _unit(k, b, h), _unit(v, b, h), er_u, tau)
+    close(score2[b:b + 1, h:h + 1], ref_score, f"C3 seeded unit ({b},{h}) kf_score")
+    got_idx = idx2[b:b + 1, h:h + 1].cpu().numpy()
+    assert np.array_equal(got_idx, O.keyformer_select(score2[b:b + 1, h:h + 1].cpu().numpy(), k_keep))
+    O.check_index_sets(got_idx, O.keyformer_select(ref_score.numpy(), k_keep), ref_score.numpy(), k_keep)
+  torch.testing.assert_close(score2.sum(-1), torch.full((B, H), float(S), device="cuda"), rtol=1e-4, atol=0.05)
+  no_timeouts(ops)
+
+
+def test_full_size_roco_units_vs_oracle(ops):
+  # configuration C4: bf16 B=2 H=40 S=4096, top-k = S/8 by mean, ties by standard deviation
+  import flashtensor_b200 as ft
+  B, S, H, k_keep = 2, 4096, 40, 512
+  q, k, v = _gpu_inputs(B, S, H, torch.bfloat16, 4)
+  out, ssum, ssq, idx = ft.RoCo(head_num=H, kv_head_num=H).select(q, k, v, k_keep)
+  torch.cuda.synchronize()
+  assert np.array_equal(idx.cpu().numpy(), O.roco_select(ssum.cpu().numpy(), ssq.cpu().numpy(), k_keep, S))
+  for b, h in [(0, 0), (1, 23)]:
+    ref_out, rs, rq = O.roco(_unit(q, b, h), _unit(k, b, h), _unit(v, b, h))
+    close(out[b:b + 1, :, h:h + 1], ref_out, f"C4 unit ({b},{h}) out")
+    close(ssum[b:b + 1, h:h + 1], rs, f"C4 unit ({b},{h}) roco_score")
+    close(ssq[b:b + 1, h:h + 1], rq, f"C4 unit ({b},{h}) roco_sq_score")
+    mean, _ = O.roco_stats(rs.numpy(), rq.numpy(), S)
+    O.check_index_sets(idx[b:b + 1, h:h + 1].cpu().numpy(), O.roco_select(rs.numpy(), rq.numpy(), k_keep, S),
+                       mean, k_keep)
+  no_timeouts(ops)
+
+
+def test_full_size_sima_units_vs_oracle(ops):
+  # configuration C5: fp16 B=8 H=32 S=8192, V ~ U(-1,1), non-causal; 16-bit and f32 outputs
+  B, S, H = 8, 8192, 32
+  q, k, v = _gpu_inputs(B, S, H, torch.float16, 5, uniform_v=True)
+  out16 = ops.sima_fwd(q, k, v)
+  torch.cuda.synchronize()
+  refs = {}
+  for b, h in [(0, 0), (5, 9), (7, 31)]:
+    refs[(b, h)] = O.sima(_unit(q, b, h), _unit(k, b, h), _unit(v, b, h))
+    close(out16[b:b + 1, :, h:h + 1], refs[(b, h)], f"C5 unit ({b},{h}) 16-bit out")
+  del out16
+  out32 = ops.sima_fwd(q, k, v, out_dtype=torch.float32)
+  torch.cuda.synchronize()
+  for (b, h), ref in refs.items():
+    close(out32[b:b + 1, :, h:h + 1], ref, f"C5 unit ({b},{h}) f32 out")
+  no_timeouts(ops)
