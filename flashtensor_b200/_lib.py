@@ -41,7 +41,8 @@ class ScoreParams(ctypes.Structure):
 
 class SelectParams(ctypes.Structure):
   _fields_ = [("score", Tensor), ("score_sq", Tensor), ("idx", Tensor), ("k_keep", ctypes.c_int32),
-              ("recent", ctypes.c_int32), ("q_len", ctypes.c_int32), ("mode", ctypes.c_int32)]
+              ("recent", ctypes.c_int32), ("q_len", ctypes.c_int32), ("mode", ctypes.c_int32),
+              ("all_rows", ctypes.c_int32), ("mean", Tensor), ("std", Tensor)]
 
 
 class SimaParams(ctypes.Structure):
@@ -60,7 +61,8 @@ class CaseParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor), ("score", Tensor),
               ("score_sq", Tensor), ("exp_rand", Tensor), ("idx", Tensor),
               ("softmax_scale", ctypes.c_float), ("tau", ctypes.c_float), ("seed", ctypes.c_uint64),
-              ("causal", ctypes.c_int32), ("k_keep", ctypes.c_int32), ("recent", ctypes.c_int32)]
+              ("causal", ctypes.c_int32), ("k_keep", ctypes.c_int32), ("recent", ctypes.c_int32),
+              ("roco_mean", Tensor), ("roco_std", Tensor)]
 
 
 class AsukaError(RuntimeError):

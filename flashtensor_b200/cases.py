@@ -228,11 +228,12 @@ class RoCo(_Case):
     self._check(q)
     return ops.roco(q, k, v, causal=self.causal)
 
-  def select(self, q, k, v, k_keep):
-    """(out, roco_score, roco_sq_score, idx): the `k_keep` keys of largest mean probability,
-    ties broken by larger standard deviation, then lower index."""
+  def select(self, q, k, v, k_keep, return_stats=False):
+    """(out, roco_score, roco_sq_score, idx[, mean, std]): the `k_keep` keys of largest mean
+    probability over the query rows that attend to them, ties broken by larger standard deviation,
+    then lower index; `return_stats` adds the per-key mean and standard deviation [B,H,Skv] f32."""
     self._check(q)
-    return ops.roco(q, k, v, causal=self.causal, k_keep=k_keep)
+    return ops.roco(q, k, v, causal=self.causal, k_keep=k_keep, return_stats=return_stats)
 
 
 class SimA(_Case):

@@ -596,7 +596,7 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   if (e != cudaSuccess) return e;
   kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 }  // namespace asuka

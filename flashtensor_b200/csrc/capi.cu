@@ -1,5 +1,6 @@
 // C-ABI layer: argument validation, tensor-map construction, launch sequencing.
 // Declarations and the reference interfaces they replace are in include/asuka_b200.h.
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstring>
@@ -16,9 +17,11 @@ static std::atomic<uint64_t> g_launches{0};
 
 uint32_t* device_status_words() {
   // one address per device; cached per device id (devices are few)
+  static std::mutex mu;
   static uint32_t* cache[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
   if (!cache[dev]) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_status_words) != cudaSuccess) return nullptr;
@@ -67,12 +70,18 @@ namespace {
 
 constexpr int kHeadDim = 128;
 
+// Every entry point calls this after its host-side validation and before its first launch.  It
+// also drops an error an earlier runtime call of this host thread may have left behind (the
+// application's or this library's), so that the status read after a launch is that launch's own.
 int check_arch() {
+  static std::mutex mu;
   static int cached[64];
   static bool have[64] = {false};
+  (void)cudaGetLastError();
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return ASUKA_ERR_CUDA;
   if (dev < 0 || dev >= 64) return ASUKA_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
   if (!have[dev]) {
     int major = 0;
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
@@ -85,9 +94,11 @@ int check_arch() {
 
 // multiprocessor count of the current device (the persistent kernels launch one CTA per SM)
 int sm_count() {
+  static std::mutex mu;
   static int cached[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  std::lock_guard<std::mutex> lock(mu);
   if (cached[dev] == 0) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
@@ -151,6 +162,12 @@ int check_qk(const asuka_tensor& q, const asuka_tensor& k, float scale, int caus
   if (k.shape[0] != q.shape[0] || k.shape[2] > q.shape[2] || q.shape[2] % k.shape[2] != 0)
     return ASUKA_ERR_BAD_SHAPE;
   if (causal && k.shape[1] < q.shape[1]) return ASUKA_ERR_BAD_SHAPE;
+  // work items and grids are counted in 32-bit integers: (batch, head) units x 128-row tiles
+  {
+    const int64_t units = q.shape[0] * q.shape[2];
+    const int64_t tiles = (std::max(q.shape[1], k.shape[1]) + 127) / 128;
+    if (units * tiles > 0x3fffffff) return ASUKA_ERR_TOO_LARGE;
+  }
   if (std::isnan(scale) || std::isinf(scale)) return ASUKA_ERR_BAD_ARGUMENT;
   o->dtype = q.dtype;
   o->s.B = static_cast<int>(q.shape[0]);
@@ -303,7 +320,9 @@ int select_impl(const asuka_select_params* p, cudaStream_t stream) {
   if (p->k_keep < 1 || p->k_keep > S - recent) return ASUKA_ERR_BAD_ARGUMENT;
   if (roco) {
     if ((r = check_dense(p->score_sq, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
-    if (p->q_len < 1 || p->q_len > S) return ASUKA_ERR_BAD_ARGUMENT;
+    if (p->q_len < 1 || (p->q_len > S && !p->all_rows)) return ASUKA_ERR_BAD_ARGUMENT;
+    if (p->mean.ptr != nullptr && (r = check_dense(p->mean, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
+    if (p->std.ptr != nullptr && (r = check_dense(p->std, ASUKA_F32, 3, sshape)) != ASUKA_OK) return r;
   }
   const int64_t ishape[3] = {B, H, p->k_keep + recent};
   if ((r = check_dense(p->idx, ASUKA_I32, 3, ishape)) != ASUKA_OK) return r;
@@ -318,6 +337,9 @@ int select_impl(const asuka_select_params* p, cudaStream_t stream) {
   a.recent = recent;
   a.q_len = p->q_len;
   a.mode = p->mode;
+  a.all_rows = roco && p->all_rows ? 1 : 0;
+  a.mean = roco ? static_cast<float*>(p->mean.ptr) : nullptr;
+  a.std = roco ? static_cast<float*>(p->std.ptr) : nullptr;
   return map_cuda(launch_select(a, stream));
 }
 
@@ -442,6 +464,8 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
     lp.k_keep = p->k_keep;
     lp.recent = p->recent;
     lp.q_len = static_cast<int32_t>(Sq);
+    lp.all_rows = p->causal ? 0 : 1;
+    if (kind == CASE_ROCO) { lp.mean = p->roco_mean; lp.std = p->roco_std; }
     lp.mode = kind == CASE_H2O ? ASUKA_SELECT_TOPK_RECENT : kind == CASE_ROCO ? ASUKA_SELECT_ROCO : ASUKA_SELECT_TOPK;
   }
 
@@ -482,7 +506,14 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
       if (recent < 0 || recent > S || p->k_keep < 1 || p->k_keep > S - recent) return ASUKA_ERR_BAD_ARGUMENT;
       const int64_t ishape[3] = {B, gqa ? Hkv : H, p->k_keep + recent};
       if ((r = check_dense(p->idx, ASUKA_I32, 3, ishape)) != ASUKA_OK) return r;
+      if (roco) {
+        const int64_t kshape[3] = {B, H, S};
+        if (p->roco_mean.ptr != nullptr && (r = check_dense(p->roco_mean, ASUKA_F32, 3, kshape)) != ASUKA_OK) return r;
+        if (p->roco_std.ptr != nullptr && (r = check_dense(p->roco_std, ASUKA_F32, 3, kshape)) != ASUKA_OK) return r;
+      }
     }
+    // the group mean runs one grid row per (batch, K/V head)
+    if (gqa && B * Hkv > 65535) return ASUKA_ERR_TOO_LARGE;
   }
 
   int r = attn_fwd_impl(&fp, nullptr, stream);
@@ -711,8 +742,10 @@ int asuka_b200_h2o_static(const asuka_case_params* p, asuka_stream stream) {
                       static_cast<double>(p->q.shape[2]);
   if (rows > static_cast<double>(ASUKA_H2O_STATIC_MAX_ROWS) || case_ws_bytes(p) > kStaticScratchBytes)
     return ASUKA_ERR_TOO_LARGE;
+  int r = check_arch();  // (before the symbol lookup, which fails on a device the image was not built for)
+  if (r != ASUKA_OK) return r;
   void* scratch = nullptr;
-  const int r = h2o_static_scratch(&scratch);
+  r = h2o_static_scratch(&scratch);
   if (r != ASUKA_OK) return r;
   return case_impl(p, CASE_H2O, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }

@@ -706,7 +706,7 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
   if (e != cudaSuccess) return e;
   kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, p);
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
@@ -720,7 +720,7 @@ cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, cons
     if (e != cudaSuccess) return e;
     kern<<<grid, kRsThreads, RsCfg<2>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
     count_launch();
-    return cudaPeekAtLastError();
+    return cudaGetLastError();
   }
   // TMA needs a 16-byte aligned base and strides that are multiples of 16 bytes
   const bool tma_ok = (reinterpret_cast<uintptr_t>(a.exp_rand) & 15u) == 0 && a.er_stride_q % 4 == 0 &&
@@ -745,7 +745,7 @@ cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, cons
     kern<<<grid, kRsThreads, RsCfg<0>::kSmem, stream>>>(mq, mk, mq, p, lse2_out);
   }
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 }  // namespace asuka

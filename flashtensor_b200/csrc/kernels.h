@@ -1,6 +1,6 @@
 // Internal launch interface between the C-ABI layer (capi.cu) and the kernel files.
 // All arguments have been validated by the caller.  Each function enqueues on `stream` and
-// returns a cudaError_t from the launch (cudaPeekAtLastError), never synchronising.
+// returns the launch's own cudaError_t (cudaGetLastError right after the launch), never synchronising.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -52,6 +52,9 @@ struct SelectArgs {
   const float* score_sq;  // or null
   int32_t* idx;           // [B*H, n_out]
   int rows, S, k_keep, recent, q_len, mode;
+  int all_rows;           // RoCo: every key is seen by all q_len rows (unmasked attention)
+  float* mean;            // RoCo, optional outputs [B*H, S]
+  float* std;
 };
 cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream);
 

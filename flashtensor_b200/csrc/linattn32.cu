@@ -231,7 +231,7 @@ cudaError_t launch_linattn32(const LinAttn32Args& a, cudaStream_t stream) {
   if (a.ea) linattn32_kernel<true><<<grid, kWarps * 32, 0, stream>>>(a);
   else linattn32_kernel<false><<<grid, kWarps * 32, 0, stream>>>(a);
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 }  // namespace asuka

@@ -67,14 +67,14 @@ cudaError_t launch_gather_kv(const GatherArgs& a, cudaStream_t stream) {
   const dim3 grid(bx, a.H, a.B);
   gather_kv_kernel<<<grid, 256, 0, stream>>>(a);
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 cudaError_t launch_group_mean(const float* in, float* out, int rows, int group, int S, cudaStream_t stream) {
   const dim3 grid((S + 255) / 256, rows);
   group_mean_kernel<<<grid, 256, 0, stream>>>(in, out, rows, group, S);
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 cudaError_t launch_pool_scores(const float* in, float* out, int rows, int S, int ksize,
@@ -82,7 +82,7 @@ cudaError_t launch_pool_scores(const float* in, float* out, int rows, int S, int
   const dim3 grid((S + 255) / 256, rows);
   pool_scores_kernel<<<grid, 256, 0, stream>>>(in, out, rows, S, ksize);
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 }  // namespace asuka

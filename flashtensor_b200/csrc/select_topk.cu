@@ -4,8 +4,8 @@
 //   TOPK          k largest keys, equal keys -> lower index first
 //   TOPK_RECENT   k largest among positions [0, S-recent), then the last `recent` positions (H2O)
 //   ROCO          key = (mean, std) with mean = sum/n_j, std = sqrt(max(sumsq/n_j - mean^2, 0)),
-//                 n_j = q_len - max(0, j - (S - q_len)); larger mean first, then larger std, then
-//                 lower index
+//                 n_j = q_len - max(0, j - (S - q_len)) (causal) or q_len (unmasked); larger mean
+//                 first, then larger std, then lower index; mean and std are optional outputs
 // One CTA per row.  Keys are mapped to order-preserving unsigned integers and kept in shared
 // memory; an MSB-first radix select (11 bits per pass: three passes for 32-bit keys, six for 64-bit
 // ones; shared-memory atomics on a 2048-bin histogram, warp-aggregated where equal digits are
@@ -38,10 +38,12 @@ template <>
 __device__ __forceinline__ uint64_t make_key<uint64_t>(const SelectArgs& a, const float* srow,
                                                        const float* qrow, int j) {
   // IEEE-exact, unfused f32 arithmetic so that the keys equal a plain f32 CPU evaluation bit for bit
-  const float n = static_cast<float>(a.q_len - max(0, j - (a.S - a.q_len)));
+  const float n = static_cast<float>(a.all_rows ? a.q_len : a.q_len - max(0, j - (a.S - a.q_len)));
   const float mean = __fdiv_rn(srow[j], n);
   const float var = fmaxf(__fsub_rn(__fdiv_rn(qrow[j], n), __fmul_rn(mean, mean)), 0.f);
   const float sd = __fsqrt_rn(var);
+  if (a.mean != nullptr) a.mean[static_cast<size_t>(blockIdx.x) * a.S + j] = mean;
+  if (a.std != nullptr) a.std[static_cast<size_t>(blockIdx.x) * a.S + j] = sd;
   return (static_cast<uint64_t>(mono_f32(mean)) << 32) | mono_f32(sd);
 }
 
@@ -208,7 +210,7 @@ cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream) {
     select_kernel<uint32_t><<<a.rows, kSelThreads, smem, stream>>>(a);
   }
   count_launch();
-  return cudaPeekAtLastError();
+  return cudaGetLastError();
 }
 
 }  // namespace asuka

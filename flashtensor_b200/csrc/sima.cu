@@ -779,7 +779,7 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     auto kern = s.bf16 ? ea_colmax_kernel<true> : ea_colmax_kernel<false>;
     kern<<<static_cast<unsigned>(bh) * pl.nchunks, 256, 0, stream>>>(sp);
     count_launch();
-    if ((e = cudaPeekAtLastError()) != cudaSuccess) return e;
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   {
     void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, StatsParams);
@@ -789,13 +789,13 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     if (e != cudaSuccess) return e;
     kern<<<static_cast<unsigned>(bh) * pl.nchunks, kStThreads, kStSmem, stream>>>(mq, mk, mv, sp);
     count_launch();
-    if ((e = cudaPeekAtLastError()) != cudaSuccess) return e;
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   {
     auto kern = s.bf16 ? sima_reduce_kernel<true> : sima_reduce_kernel<false>;
     kern<<<bh * kRedBlocks, 256, 0, stream>>>(sp);
     count_launch();
-    if ((e = cudaPeekAtLastError()) != cudaSuccess) return e;
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   {
     CUtensorMap mm;
@@ -828,7 +828,7 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     if (e != cudaSuccess) return e;
     kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads + (s.ea ? 256 : 0), out_smem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);
     count_launch();
-    e = cudaPeekAtLastError();
+    e = cudaGetLastError();
   }
   return e;
 }

@@ -13,17 +13,16 @@ typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline encode_tiled_fn get_encode_fn() {
-  static encode_tiled_fn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // resolved once per process; the initialisation of a function-local static is thread-safe
+  static const encode_tiled_fn fn = [] {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<encode_tiled_fn>(p);
+      return reinterpret_cast<encode_tiled_fn>(p);
     }
-  }
+    return static_cast<encode_tiled_fn>(nullptr);
+  }();
   return fn;
 }
 

@@ -120,18 +120,25 @@ def keyformer_rowstat(q, k, causal=True, softmax_scale=0.0, exp_rand=None, tau=1
   return lse
 
 
-def select_topk(score, k_keep, mode=_lib.SELECT_TOPK, recent=0, score_sq=None, q_len=0):
-  """Kept key indices, ascending int32 [B,H,k_keep(+recent)]."""
+def select_topk(score, k_keep, mode=_lib.SELECT_TOPK, recent=0, score_sq=None, q_len=0, causal=True,
+                return_stats=False):
+  """Kept key indices, ascending int32 [B,H,k_keep(+recent)].  Mode SELECT_ROCO ranks by the
+  per-key mean (then standard deviation) of the probabilities over the rows that attend to the
+  key -- all `q_len` rows when `causal` is False -- and with `return_stats` also returns
+  (mean, std), both [B,H,S] f32."""
   lib = _lib.load()
   _same_device(score, score_sq)
   B, H, _ = score.shape
   n_out = k_keep + (recent if mode == _lib.SELECT_TOPK_RECENT else 0)
   with _on(score.device):
     idx = torch.empty((B, H, n_out), dtype=torch.int32, device=score.device)
+    stats = return_stats and mode == _lib.SELECT_ROCO
+    mean = torch.empty_like(score) if stats else None
+    std = torch.empty_like(score) if stats else None
     p = _lib.SelectParams(_desc(score), _desc(score_sq), _desc(idx), int(k_keep), int(recent),
-                          int(q_len), int(mode))
+                          int(q_len), int(mode), int(not causal), _desc(mean), _desc(std))
     _lib.check("asuka_b200_select_topk", lib.asuka_b200_select_topk(ctypes.byref(p), _stream(score)))
-  return idx
+  return (idx, mean, std) if stats else idx
 
 
 def pool_scores(score, kernel_size):
@@ -196,7 +203,8 @@ def linattn32_fwd(q, k, v, ea=False, out=None):
 
 
 def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None, tau=1.0, seed=0,
-          k_keep=0, recent=0, n_idx=0, workspace=None, out=None, score=None, score_sq=None, idx=None):
+          k_keep=0, recent=0, n_idx=0, workspace=None, out=None, score=None, score_sq=None, idx=None,
+          roco_mean=None, roco_std=None):
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
   _same_device(q4, k4, v4, exp_rand)
@@ -214,7 +222,8 @@ def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None,
       idx = torch.empty((B, H, n_idx), dtype=torch.int32, device=dev)
     p = _lib.CaseParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(score),
                         _desc(score_sq), _desc(exp_rand), _desc(idx), float(softmax_scale),
-                        float(tau), int(seed), int(bool(causal)), int(k_keep), int(recent))
+                        float(tau), int(seed), int(bool(causal)), int(k_keep), int(recent),
+                        _desc(roco_mean), _desc(roco_std))
     if workspace is None:
       nbytes = ctypes.c_size_t(0)
       _lib.check("asuka_b200_case_workspace_bytes",
@@ -249,15 +258,24 @@ def h2o_static(q, k, v, out, score, idx=None, causal=True, softmax_scale=0.0, k_
   with _on(q4.device):
     p = _lib.CaseParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(score),
                         _lib.Tensor(), _lib.Tensor(), _desc(idx), float(softmax_scale), 1.0, 0,
-                        int(bool(causal)), int(k_keep), int(recent))
+                        int(bool(causal)), int(k_keep), int(recent), _lib.Tensor(), _lib.Tensor())
     _lib.check("asuka_b200_h2o_static", lib.asuka_b200_h2o_static(ctypes.byref(p), _stream(q4)))
   return (out, score, idx) if idx is not None else (out, score)
 
 
-def roco(q, k, v, causal=True, softmax_scale=0.0, k_keep=0, **buffers):
-  """(out, roco_score, roco_sq_score[, idx]) -- cases/kernels/roco.py:18-48."""
+def roco(q, k, v, causal=True, softmax_scale=0.0, k_keep=0, return_stats=False, **buffers):
+  """(out, roco_score, roco_sq_score[, idx[, mean, std]]) -- cases/kernels/roco.py:18-48; with a
+  selection (`k_keep` > 0) and `return_stats`, also the per-key mean and standard deviation of the
+  probabilities the selection ranks by, [B,H,Skv] f32."""
+  if return_stats and k_keep > 0:
+    k4 = _as4d(k)
+    shape = (k4.shape[0], _as4d(q).shape[2], k4.shape[1])
+    buffers.setdefault("roco_mean", torch.empty(shape, dtype=torch.float32, device=q.device))
+    buffers.setdefault("roco_std", torch.empty(shape, dtype=torch.float32, device=q.device))
   out, score, sq, idx = _case("asuka_b200_roco", q, k, v, causal, softmax_scale, want_sq=True,
                               k_keep=k_keep, n_idx=k_keep, **buffers)
+  if return_stats and k_keep > 0:
+    return out, score, sq, idx, buffers["roco_mean"], buffers["roco_std"]
   return (out, score, sq, idx) if k_keep else (out, score, sq)
 
 

@@ -131,8 +131,13 @@ typedef struct {
   asuka_tensor idx;      /* [B, H, k_keep (+ recent)] i32 out, ascending */
   int32_t k_keep;
   int32_t recent; /* mode TOPK_RECENT */
-  int32_t q_len;  /* mode ROCO: n_j = q_len - max(0, j - (S - q_len)) */
+  int32_t q_len;  /* mode ROCO: n_j = q_len - max(0, j - (S - q_len)), the number of query rows
+                     that attend to key j under the causal mask */
   int32_t mode;   /* asuka_select_mode */
+  int32_t all_rows; /* mode ROCO: 1 = the scores come from unmasked attention, every key is seen by
+                       all q_len rows (n_j = q_len); 0 = causal count above */
+  asuka_tensor mean; /* mode ROCO, optional (ptr may be NULL): [B, H, S] f32 out, sum_j / n_j */
+  asuka_tensor std;  /* mode ROCO, optional: [B, H, S] f32 out, sqrt(max(sumsq_j / n_j - mean_j^2, 0)) */
 } asuka_select_params;
 
 int asuka_b200_select_topk(const asuka_select_params* p, asuka_stream stream);
@@ -188,7 +193,10 @@ typedef struct {
 int asuka_b200_linattn32_fwd(const asuka_linattn32_params* p, asuka_stream stream);
 
 /* ---- fused cases: forward + column scores (+ selection) enqueued back to back on one stream.
- *      `workspace` holds the row statistic between the two kernels: B*H*Sq floats. ---- */
+ *      `workspace` holds the row statistics between the kernels: two arrays of B*H*Sq floats
+ *      (unperturbed and Keyformer's perturbed one), each rounded up to 256 bytes, plus, when k
+ *      and v have fewer heads than q, B*H*Skv floats for the per-query-head scores ahead of the
+ *      group mean.  asuka_b200_case_workspace_bytes gives the exact figure. ---- */
 typedef struct {
   asuka_tensor q, k, v, out;
   asuka_tensor score;    /* h2o_score | kf_score | roco_score, [B, H, Skv] f32 */
@@ -201,6 +209,8 @@ typedef struct {
   int32_t causal;
   int32_t k_keep;
   int32_t recent;
+  asuka_tensor roco_mean; /* RoCo with idx only, optional: per-key mean of the probabilities over the */
+  asuka_tensor roco_std;  /* rows that attend to the key, and their standard deviation; [B, H, Skv] f32 */
 } asuka_case_params;
 
 int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes);
@@ -230,6 +240,9 @@ int asuka_b200_keyformer(const asuka_case_params* p, void* workspace, size_t wor
  * Limits and rules:
  *  - B * H * Sq must not exceed ASUKA_H2O_STATIC_MAX_ROWS; larger problems are refused with
  *    ASUKA_ERR_TOO_LARGE before anything is launched (use asuka_b200_h2o with a workspace).
+ *  - With grouped-query inputs (k and v with fewer heads than q) the per-query-head scores are
+ *    parked in the same array ahead of the group mean: 8 * B*H*Sq + 4 * B*H*Skv bytes (each part
+ *    rounded up to 256) must fit in the array's 4 MiB, or the call is refused the same way.
  *  - The array (4 MiB) occupies memory on every GPU that loads the library, until the process exits.
  *  - The first call on each device looks up the array's device address (the device must be current,
  *    as for every call here) and remembers it.  Make that first call ahead of any stream capture.

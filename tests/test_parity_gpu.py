@@ -503,6 +503,114 @@ def test_errors_raise_and_leave_the_device_usable(ops):
   no_timeouts(ops)
 
 
+class _Banded:
+  """Tensors carved out of one pattern-filled device buffer with untouched bands around each, to
+  catch stores that land outside an output or a workspace (the ragged ends are the risk)."""
+  BAND = 8192
+
+  def __init__(self, total_bytes):
+    self.buf = torch.full((total_bytes,), 0xA5, dtype=torch.uint8, device="cuda")
+    self.off = self.BAND
+    self.spans = []
+
+  def take(self, shape, dtype):
+    n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+    assert self.off + n + self.BAND <= self.buf.numel()
+    t = self.buf[self.off:self.off + n].view(dtype).view(*shape)
+    self.spans.append((self.off, self.off + n))
+    self.off += (n + self.BAND + 255) // 256 * 256
+    return t
+
+  def bands_untouched(self):
+    keep = torch.ones(self.buf.numel(), dtype=torch.bool, device="cuda")
+    for lo, hi in self.spans:
+      keep[lo:hi] = False
+    return bool((self.buf[keep] == 0xA5).all())
+
+
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[1] * s[2] > 1] + [(1, 130, 130, 1, True)])
+def test_no_store_lands_outside_outputs_or_workspace(ops, shape):
+  import ctypes
+  from flashtensor_b200 import _lib
+  B, Sq, Skv, H, causal = shape
+  q, k, v = (t.cuda() for t in O.make_inputs("roco", B, Sq, Skv, H, 128, torch.bfloat16, seed=5))
+  k_keep = max(1, Skv // 8)
+  recent = min(16, Skv - k_keep)
+  mem = _Banded(64 << 20)
+  lib = _lib.load()
+
+  def ws_for(**kw):
+    p = _lib.CaseParams(ops._desc(q), ops._desc(k), ops._desc(v))
+    n = ctypes.c_size_t(0)
+    assert lib.asuka_b200_case_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
+    return mem.take((n.value,), torch.uint8)
+
+  # H2O with the recent window, RoCo with statistics, Keyformer with both noise sources
+  o1, s1, i1 = ops.h2o(q, k, v, causal=causal, k_keep=k_keep, recent=recent, workspace=ws_for(),
+                       out=mem.take((B, Sq, H, 128), torch.bfloat16), score=mem.take((B, H, Skv), torch.float32),
+                       idx=mem.take((B, H, k_keep + recent), torch.int32))
+  r = ops.roco(q, k, v, causal=causal, k_keep=k_keep, return_stats=True, workspace=ws_for(),
+               out=mem.take((B, Sq, H, 128), torch.bfloat16), score=mem.take((B, H, Skv), torch.float32),
+               score_sq=mem.take((B, H, Skv), torch.float32), idx=mem.take((B, H, k_keep), torch.int32),
+               roco_mean=mem.take((B, H, Skv), torch.float32), roco_std=mem.take((B, H, Skv), torch.float32))
+  er = 1 + torch.randn(B, H, Sq, Skv, device="cuda").abs()
+  k1 = ops.keyformer(q, k, v, er, tau=1.5, causal=causal, k_keep=k_keep, workspace=ws_for(),
+                     out=mem.take((B, Sq, H, 128), torch.bfloat16), score=mem.take((B, H, Skv), torch.float32),
+                     idx=mem.take((B, H, k_keep), torch.int32))
+  k2 = ops.keyformer(q, k, v, None, tau=1.5, seed=11, causal=causal, k_keep=k_keep, workspace=ws_for(),
+                     out=mem.take((B, Sq, H, 128), torch.bfloat16), score=mem.take((B, H, Skv), torch.float32),
+                     idx=mem.take((B, H, k_keep), torch.int32))
+  o5 = ops.attn_fwd(q, k, v, causal=causal, out=mem.take((B, Sq, H, 128), torch.bfloat16))
+  torch.cuda.synchronize()
+  assert mem.bands_untouched(), "a kernel wrote outside its outputs or workspace"
+  # and the banded buffers hold the same results as freshly allocated ones
+  ref = ops.h2o(q, k, v, causal=causal, k_keep=k_keep, recent=recent)
+  assert torch.equal(o1, ref[0]) and torch.equal(s1, ref[1]) and torch.equal(i1, ref[2])
+  assert torch.equal(o5, ref[0]) and torch.equal(r[0], ref[0]) and torch.equal(k1[0], ref[0]) and torch.equal(k2[0], ref[0])
+  # SimA / EA with their workspaces (16-bit output through TMA stores, f32 output through plain stores)
+  if Sq == Skv:
+    for entry in ("asuka_b200_sima_fwd", "asuka_b200_ea_fwd"):
+      for odt in (torch.bfloat16, torch.float32):
+        out = mem.take((B, Sq, H, 128), odt)
+        p = _lib.SimaParams(ops._desc(q), ops._desc(k), ops._desc(v), ops._desc(out))
+        n = ctypes.c_size_t(0)
+        assert lib.asuka_b200_sima_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
+        ws = mem.take((max(n.value, 256),), torch.uint8)
+        st = getattr(lib, entry)(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws.numel()),
+                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert st == 0
+    torch.cuda.synchronize()
+    assert mem.bands_untouched(), "a SimA / EA kernel wrote outside its outputs or workspace"
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_roco_mean_and_std_outputs(ops, causal):
+  # the per-key mean and standard deviation the selection ranks by, as tensors: bit-exact against
+  # the oracle's plain f32 evaluation on the kernel's own sums, within tolerance against the oracle's
+  import flashtensor_b200 as ft
+  from flashtensor_b200 import _lib
+  for (B, Sq, Skv, H) in [(2, 384, 384, 3), (1, 200, 456, 2)]:
+    q, k, v = O.make_inputs("roco", B, Sq, Skv, H, 128, torch.bfloat16, seed=Sq)
+    k_keep = Skv // 8
+    model = ft.RoCo(head_num=H, kv_head_num=H, causal=causal)
+    out, ssum, ssq, idx, mean, std = model.select(q.cuda(), k.cuda(), v.cuda(), k_keep, return_stats=True)
+    torch.cuda.synchronize()
+    want_mean, want_std = O.roco_stats(ssum.cpu().numpy(), ssq.cpu().numpy(), Sq, causal)
+    assert np.array_equal(mean.cpu().numpy(), want_mean) and np.array_equal(std.cpu().numpy(), want_std)
+    assert np.array_equal(idx.cpu().numpy(), O.roco_select(ssum.cpu().numpy(), ssq.cpu().numpy(), k_keep, Sq, causal))
+    _, rs, rq = O.roco(q, k, v, causal)
+    ref_mean, ref_std = O.roco_stats(rs.numpy(), rq.numpy(), Sq, causal)
+    close(mean, torch.from_numpy(ref_mean), "roco mean")
+    close(std, torch.from_numpy(ref_std), "roco std")
+    O.check_index_sets(idx.cpu().numpy(), O.roco_select(rs.numpy(), rq.numpy(), k_keep, Sq, causal), ref_mean, k_keep)
+    # the stand-alone selection entry gives the same
+    idx2, mean2, std2 = ops.select_topk(ssum, k_keep, mode=_lib.SELECT_ROCO, score_sq=ssq, q_len=Sq,
+                                        causal=causal, return_stats=True)
+    assert torch.equal(idx2, idx) and torch.equal(mean2, mean) and torch.equal(std2, std)
+  no_timeouts(ops)
+
+
 # ------------------------------------------------------------------------------------------
 # (3) full benchmark sizes: size-independent properties
 # ------------------------------------------------------------------------------------------

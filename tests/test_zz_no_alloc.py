@@ -3,16 +3,18 @@
 It exists for hosts that cannot give the library scratch memory and cannot let it allocate
 (engine plug-ins whose enqueue hook must not allocate, processes whose memory pool already owns
 the whole device).  Its scratch is a fixed array inside the library, shared by all calls, so the
-check runs two calls back to back and compares each with the ordinary entry point
-(asuka_b200_h2o, caller-supplied workspace) on the same inputs.  This file is named to be
-collected last: a run that stops at the first failure has then already run every other test.
+check runs calls back to back and compares each with the ordinary entry point (asuka_b200_h2o,
+caller-supplied workspace) on the same inputs, and with the CPU oracle.  The shapes include
+grouped K/V heads (which park more in the array) and the largest problem the array admits.
 """
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
 from flashtensor_b200 import _lib
+from oracle import attn_oracle as O
 
 
 def _desc(t):
@@ -50,6 +52,12 @@ def test_static_entry_refuses_oversized_requests_before_any_launch(built_lib):
     assert lib.asuka_b200_h2o_static(ctypes.byref(p), None) == want
   assert rows_ok == 524288  # ASUKA_H2O_STATIC_MAX_ROWS in include/asuka_b200.h
   assert lib.asuka_b200_h2o_static(None, None) == -1
+  # grouped K/V heads: 8 bytes per query row plus 4 bytes per (query head, key) must fit in 4 MiB
+  B, S, H, Hkv = 1, 32768, 12, 4          # 393216 rows: 3 MiB of row statistics + 1.5 MiB of scores
+  p = _lib.CaseParams(fake((B, S, H, 128)), fake((B, S, Hkv, 128)), fake((B, S, Hkv, 128)),
+                      fake((B, S, H, 128)), fake((B, Hkv, S), 2), _lib.Tensor(), _lib.Tensor(),
+                      _lib.Tensor(), 0.0, 1.0, 0, 1, 0, 0)
+  assert lib.asuka_b200_h2o_static(ctypes.byref(p), None) == -11
 
 
 @pytest.mark.gpu
@@ -59,14 +67,17 @@ def test_static_entry_matches_workspace_entry_twice_in_a_row(built_lib):
   dev = torch.device("cuda", 0)
   stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
   g = torch.Generator(device=dev).manual_seed(123)
-  for call, (B, S, H, k_keep, recent) in enumerate([(1, 1024, 4, 128, 64), (2, 640, 3, 80, 32)]):
-    q, k, v = (torch.randn(B, S, H, 128, generator=g, device=dev).half() for _ in range(3))
+  # (B, S, H, Hkv, k_keep, recent); the last shape is exactly ASUKA_H2O_STATIC_MAX_ROWS query rows
+  shapes = [(1, 1024, 4, 4, 128, 64), (2, 640, 3, 3, 80, 32), (1, 777, 6, 2, 90, 40), (4, 4096, 32, 32, 512, 256)]
+  for call, (B, S, H, Hkv, k_keep, recent) in enumerate(shapes):
+    q = torch.randn(B, S, H, 128, generator=g, device=dev).half()
+    k, v = (torch.randn(B, S, Hkv, 128, generator=g, device=dev).half() for _ in range(2))
     res = []
     for static in (False, True):
       # the caller owns every output; poison them so that stale data cannot pass
       out = torch.full((B, S, H, 128), float("nan"), dtype=torch.float16, device=dev)
-      score = torch.full((B, H, S), -1.0, dtype=torch.float32, device=dev)
-      idx = torch.full((B, H, k_keep + recent), -7, dtype=torch.int32, device=dev)
+      score = torch.full((B, Hkv, S), -1.0, dtype=torch.float32, device=dev)
+      idx = torch.full((B, Hkv, k_keep + recent), -7, dtype=torch.int32, device=dev)
       p = _params(q, k, v, out, score, idx, k_keep, recent)
       if static:
         st = lib.asuka_b200_h2o_static(ctypes.byref(p), stream)
@@ -84,5 +95,18 @@ def test_static_entry_matches_workspace_entry_twice_in_a_row(built_lib):
     assert (o0.float() - o1.float()).abs().max().item() <= 2e-2, f"call {call}: out differs"
     assert (s0 - s1).abs().max().item() <= 2e-2 and ((s0 - s1).abs().max() / s0.abs().max()).item() <= 1e-2
     assert torch.equal(i0, i1), f"call {call}: kept indices differ"
+    # against the CPU oracle: the whole problem when it is small, two units of the largest one
+    units = [(b, h) for b in range(B) for h in range(Hkv)] if B * S * H <= 16384 else [(0, 0), (B - 1, Hkv - 1)]
+    grp = H // Hkv
+    for b, h in units:
+      ref_out, ref_score = O.h2o_gqa(q[b:b + 1, :, h * grp:(h + 1) * grp].cpu(), k[b:b + 1, :, h:h + 1].cpu(),
+                                     v[b:b + 1, :, h:h + 1].cpu())
+      e = O.errors(o1[b:b + 1, :, h * grp:(h + 1) * grp], ref_out)
+      assert e["abs_max"] <= 2e-2 and e["scale_rel"] <= 1e-2, (call, b, h, e)
+      e = O.errors(s1[b:b + 1, h:h + 1], ref_score)
+      assert e["abs_max"] <= 2e-2 and e["scale_rel"] <= 1e-2, (call, b, h, e)
+      O.check_index_sets(i1[b:b + 1, h:h + 1, :k_keep].cpu().numpy(),
+                         O.h2o_select(ref_score.numpy(), k_keep, recent)[..., :k_keep], ref_score.numpy(),
+                         k_keep, S - recent)
   w = (ctypes.c_uint32 * 2)()
   assert lib.asuka_b200_device_status(w) == 0
