@@ -364,7 +364,7 @@ def main():
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=20)
   ap.add_argument("--warmup", type=int, default=10)
-  ap.add_argument("--repeats", type=int, default=0, help="timed loops of --steps calls (0: enough for ~0.5 s, at least 10)")
+  ap.add_argument("--repeats", type=int, default=0, help="timed loops of --steps calls (0: ten)")
   ap.add_argument("--case", default="h2o", choices=sorted(WORKLOADS))
   ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
   ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
@@ -461,7 +461,9 @@ def main():
       step(*sets[i % n_sets])
     torch.cuda.synchronize()
     est_ms = (time.time() - t0) / 3 * 1e3
-    repeats = args.repeats if args.repeats > 0 else max(10, min(200, int(500.0 / max(args.steps * est_ms, 1e-3))))
+    # ten loops by default: long enough for a median and a spread, short enough (~0.1 s) that the
+    # clocks are those of a burst, like the measured peak the roofline divides by
+    repeats = args.repeats if args.repeats > 0 else 10
     if world > 1:   # every rank must run the same number of loops
       t = torch.tensor([repeats], device=device)
       dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -541,7 +543,7 @@ def main():
       kern(i)
     barrier()
     reps, t_begin = [], time.time()
-    for _ in range(max(10, min(50, main_mode["repeats"]))):
+    for _ in range(10):
       ms_k, _, _ = timed_loop(kern, args.steps)
       reps.append(ms_k / args.steps * 1e3)
     sampler.window(t_begin, time.time())

@@ -18,8 +18,8 @@
 //   warps 8-11    softmax of tile 1
 // TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 f32 columns each; P_t (16-bit, 64 columns)
 // overwrites the front of S_t once S_t is in registers.  The exponent reference of a row is only
-// moved when a tile's row sum would overflow the stale one, so O is rescaled (a TMEM round trip)
-// almost never.  The epilogue writes O_t / l from registers straight to global memory.
+// taken from the first tile's true row maximum and then only moved when a later tile's row sum
+// would overflow the stale one, so O is rescaled (a TMEM round trip) almost never.  The epilogue writes O_t / l from registers straight to global memory.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -66,6 +66,12 @@ struct Bars {
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
 }
 
@@ -197,6 +203,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
+  // The set-up above may have run while the kernel ahead in the stream was still draining; q, k and
+  // v may be that kernel's outputs and out / lse its inputs, so nothing is read or written before
+  // it has finished.  The kernel behind this one (the column pass) may be scheduled from now on:
+  // its CTAs come up on SMs whose forward CTA has retired and wait there for this grid's end.
+  griddep_wait();
+  griddep_launch_dependents();
 
   // Every role walks the same item list and keeps running counts (K tiles, V tiles, tile steps,
   // items per tile) from which ring stages and barrier parities follow; nothing is reset
@@ -405,10 +417,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int thr = lim - j * kTile;  // columns > thr of this tile are masked for this row
 
         // The whole 128-wide row is exponentiated at once against the reference left by earlier
-        // tiles, so the MUFU starts right after the TMEM load and runs without a gap; the largest
-        // tile's row sum is looked at afterwards.  If it exceeds 2^13 -- or is not finite, as in the
-        // very first tile, which has no reference yet -- the rare path takes the true maximum, moves the
-        // reference up, rescales what was accumulated under the old one and redoes the tile.
+        // tiles, so the MUFU starts right after the TMEM load and runs without a gap; the tile's
+        // row sum is looked at afterwards.  If it exceeds 2^13 (or is not finite) the rare path
+        // takes the true maximum, moves the reference up, rescales what was accumulated under the
+        // old one and redoes the tile.
         float e[128];
         {
           uint32_t(&u)[128] = *reinterpret_cast<uint32_t(*)[128]>(e);
@@ -427,24 +439,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 128; ++i) e[i] = (i > thr) ? -INFINITY : e[i];
         }
-        {
-          const float mul = kCap ? p.cap_out : scale;
-          const float neg_m = -m_ref;
+        if (j == 0) {
+          // the first tile of an item has no reference yet: take the tile's true row maximum (the
+          // capped and scaled logit is monotone in the raw one) instead of exponentiating blind
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int i = 0; i < 128; ++i) e[i] = ex2(fmaf(e[i], mul, neg_m));
+          for (int i = 0; i < 128; i += 8) {
+            mx4[0] = max3(mx4[0], e[i], e[i + 1]);
+            mx4[1] = max3(mx4[1], e[i + 2], e[i + 3]);
+            mx4[2] = max3(mx4[2], e[i + 4], e[i + 5]);
+            mx4[3] = max3(mx4[3], e[i + 6], e[i + 7]);
+          }
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          m_ref = mx > -INFINITY ? mx * (kCap ? p.cap_out : scale) : 0.f;
+        }
+        {
+          // two logits per FMA instruction (packed f32x2): the softmax warp of a tile runs alone on
+          // its scheduler and is bound by the number of instructions it has to issue
+          const float mul = kCap ? p.cap_out : scale;
+          const float2 mul2 = make_float2(mul, mul), neg_m2 = make_float2(-m_ref, -m_ref);
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float2 x = __ffma2_rn(make_float2(e[2 * i], e[2 * i + 1]), mul2, neg_m2);
+            e[2 * i] = ex2(x.x);
+            e[2 * i + 1] = ex2(x.y);
+          }
         }
         // The tile's row sum doubles as the overflow probe: it bounds every term from above, and it
-        // is NaN or infinite exactly when some term is (first tile: no reference yet).  P is packed
+        // is NaN or infinite exactly when some term is.  P is packed
         // to 16 bits right away (the compiler interleaves it with the exponentials), so that only
         // the TMEM store is left once the probe has passed.
-        float ts8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float2 ts4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         uint32_t pk[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          ts8[i & 7] += e[2 * i] + e[2 * i + 1];
+          ts4[i & 3] = __fadd2_rn(ts4[i & 3], make_float2(e[2 * i], e[2 * i + 1]));
           pk[i] = pack2<kBF16>(e[2 * i], e[2 * i + 1]);
         }
-        float tile_sum = ((ts8[0] + ts8[1]) + (ts8[2] + ts8[3])) + ((ts8[4] + ts8[5]) + (ts8[6] + ts8[7]));
+        const float2 ts2 = __fadd2_rn(__fadd2_rn(ts4[0], ts4[1]), __fadd2_rn(ts4[2], ts4[3]));
+        float tile_sum = ts2.x + ts2.y;
         const bool need = !(tile_sum <= kRescaleLimit);
         if (__any_sync(0xffffffffu, need)) {
           // ---- rare: the raw logits are still intact in TMEM; take their maximum, 32 columns at a time
@@ -464,7 +497,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const float mx2 = kCap ? tanh_approx(mx * p.cap_in) * p.cap_out : mx * scale;
           float alpha = 1.f;
           if (need) {
-            alpha = ex2(m_ref - mx2);  // 0 when there was no reference yet
+            alpha = ex2(m_ref - mx2);
             m_ref = mx2;
             l *= alpha;
           }
@@ -594,9 +627,9 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   if (e != cudaSuccess) return e;
   e = check_register_budget(reinterpret_cast<const void*>(kern), kThreads, 128 * kUtilRegs + 256 * kSoftmaxRegs);
   if (e != cudaSuccess) return e;
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
+  e = launch_dependent(kern, grid, dim3(kThreads), kSmemBytes, stream, mq, mk, mv, p);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace asuka

@@ -279,11 +279,13 @@ int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a)
   return check_arch();
 }
 
-int col_scores_impl(const asuka_score_params* p, cudaStream_t stream) {
+// `chained`: the kernel ahead in the stream is one of this library's that writes neither q nor k
+int col_scores_impl(const asuka_score_params* p, cudaStream_t stream, bool chained = false) {
   QKV c;
   ScoreArgs a;
   int r = prep_scores(p, false, &c, &a);
   if (r != ASUKA_OK) return r;
+  a.chained = chained ? 1 : 0;
   CUtensorMap mq, mk;
   if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k))) return r;
   return map_cuda(launch_col_scores(mq, mk, a, c.s, stream));
@@ -521,7 +523,7 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
   if (kind == CASE_KF) {
     if ((r = kf_rowstat_impl(&sp, stream)) != ASUKA_OK) return r;
   }
-  if ((r = col_scores_impl(&sp, stream)) != ASUKA_OK) return r;
+  if ((r = col_scores_impl(&sp, stream, true)) != ASUKA_OK) return r;
   if (gqa) {
     r = map_cuda(launch_group_mean(head_scores, static_cast<float*>(p->score.ptr), static_cast<int>(B * Hkv),
                                    static_cast<int>(H / Hkv), static_cast<int>(p->k.shape[1]), stream));

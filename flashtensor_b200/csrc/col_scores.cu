@@ -56,6 +56,7 @@ struct ColParams {
   int64_t er_sb, er_sh, er_sq;
   uint64_t seed;
   uint32_t* status;
+  int chained;        // the kernel ahead in the stream does not write q or k
 };
 
 struct ColBars {
@@ -74,6 +75,74 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// exp2 on the FMA pipe, two logits per instruction (packed f32x2): x = n + f with n = rint(x) taken
+// from the mantissa of x + 1.5 * 2^23, a degree-4 polynomial for 2^f on [-0.5, 0.5] (relative
+// error 2.7e-6), and n added into the exponent field.  The MUFU does 16 exponentials per clock per
+// SM and is what bounds this kernel; giving a share of every tile's logits to the FMA pipe (128
+// lanes per clock) lets both pipes run side by side.  The share is small: each such logit costs
+// about 7 clocks of the FMA pipe per warp (packed instructions occupy it for two) against 8 of the
+// MUFU, and the pipe also carries the scaling and the accumulation of every logit.  Inputs below -120 give 2^-120 (the column
+// sums do not notice); inputs above 0 only occur at masked positions, which are zeroed afterwards.
+#ifndef ASUKA_COL_POLY_QUARTERS
+#define ASUKA_COL_POLY_QUARTERS 1  // of every four logits, how many go to the FMA pipe (0, 1, 2 or 3);
+                                   // measured at S = 4096, 32 heads: 0 -> 96.9, 1 -> 91.3, 2 -> 92.7 us
+#endif
+#ifndef ASUKA_COL_POLY_DEG
+#define ASUKA_COL_POLY_DEG 4
+#endif
+#ifndef ASUKA_COL_POLY_SCALAR
+#define ASUKA_COL_POLY_SCALAR 0
+#endif
+__device__ __forceinline__ float ex2_fma_pipe1(float x) {
+#ifndef ASUKA_COL_POLY_NOCLAMP
+  x = fmaxf(x, -120.f);
+#endif
+  const float t = __fadd_rn(x, 12582912.f);
+  const float n = __fadd_rn(t, -12582912.f);
+  const float f = __fadd_rn(x, -n);
+#if ASUKA_COL_POLY_DEG == 3
+  float p = 0.055171605199575424f;
+  p = __fmaf_rn(p, f, 0.2426111102104187f);
+  p = __fmaf_rn(p, f, 0.6932609677314758f);
+  p = __fmaf_rn(p, f, 0.9999280571937561f);
+#else
+  float p = 0.009570094756782055f;
+  p = __fmaf_rn(p, f, 0.05591785907745361f);
+  p = __fmaf_rn(p, f, 0.240247443318367f);
+  p = __fmaf_rn(p, f, 0.6931217908859253f);
+  p = __fmaf_rn(p, f, 0.9999992847442627f);
+#endif
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+__device__ __forceinline__ float2 ex2_fma_pipe(float2 x) {
+#if ASUKA_COL_POLY_SCALAR
+  return make_float2(ex2_fma_pipe1(x.x), ex2_fma_pipe1(x.y));
+#else
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+#ifndef ASUKA_COL_POLY_NOCLAMP
+  x.x = fmaxf(x.x, -120.f);
+  x.y = fmaxf(x.y, -120.f);
+#endif
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+#if ASUKA_COL_POLY_DEG == 3
+  float2 p = make_float2(0.055171605199575424f, 0.055171605199575424f);
+  p = __ffma2_rn(p, f, make_float2(0.2426111102104187f, 0.2426111102104187f));
+  p = __ffma2_rn(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+  p = __ffma2_rn(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+#else
+  float2 p = make_float2(0.009570094756782055f, 0.009570094756782055f);
+  p = __ffma2_rn(p, f, make_float2(0.05591785907745361f, 0.05591785907745361f));
+  p = __ffma2_rn(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
+  p = __ffma2_rn(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+  p = __ffma2_rn(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+#endif
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
+#endif
+}
+
 // Seeded Keyformer noise: one bijective 32-bit mix ("lowbias32") per logit.
 //   head_key = hash(seed_lo ^ hash((b*H + h) ^ seed_hi));  word = hash(((q << 16) ^ kv) ^ head_key)
 //   u = ((word >> 9) + 0.5) * 2^-23 in (0,1);  exp_rand = -ln(u);  noise g = -ln(exp_rand) ~ Gumbel(0,1)
@@ -113,7 +182,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const ColParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) ColBars bars;
-  __shared__ __align__(16) float lse_s[kQStages][kTile];
+  __shared__ __align__(16) float lse_s[kQStages][kTile];  // minus the row statistic
   __shared__ float part_s[2][2][2][kTile];  // [sum, sum of squares][query half][key tile][key]
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
@@ -139,6 +208,13 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   for (int t = 0; t < 2; ++t) i_start[t] = p.causal ? max(0, kv0[t] - p.diag_off) / kTile : 0;
   const int i_begin = i_start[0];
   const int n_active = (active[0] ? 1 : 0) + (active[1] ? 1 : 0);
+
+  // Launched as a programmatic dependent: unless the caller vouches for the kernel ahead (the fused
+  // case entry points, whose forward kernel writes only the output and the row statistic), q and k
+  // may still be in the making, and everything waits.  Otherwise only the producer waits, before
+  // its first read of the row statistic, and the set-up and the K loads run under that kernel's tail.
+  if (!p.chained) griddep_wait();
+  griddep_launch_dependents();
 
   if (tid == 0) {
     abort_s = 0;
@@ -182,6 +258,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------------ producer (whole warp)
     const float* lse_row = p.lse2 + (static_cast<size_t>(b) * p.H + h) * p.Sq;
     bool ok = true;
+    if (p.chained) griddep_wait();  // the row statistic is the output of the kernel ahead
     for (int i = i_begin; i < p.nq_tiles; ++i) {
       const int c = i - i_begin;
       const int st = c % kQStages;
@@ -190,11 +267,12 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_empty[st]), (use - 1) & 1, abortp));
         if (!ok) { if (lane == 0) record_timeout(p.status, 21); break; }
       }
-      // row statistics of this query tile; rows past the end get +inf so that exp2 gives 0
+      // NEGATED row statistics of this query tile (they are only ever subtracted); rows past the
+      // end get -inf so that exp2 gives 0
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const int qi = i * kTile + r * 32 + lane;
-        lse_s[st][r * 32 + lane] = qi < p.Sq ? __ldg(lse_row + qi) : INFINITY;
+        lse_s[st][r * 32 + lane] = qi < p.Sq ? -__ldg(lse_row + qi) : -INFINITY;
       }
       __syncwarp();
       if (lane == 0) {
@@ -327,17 +405,17 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
               const float4 L = lse4[ch * 8 + g];
-              const float lv[4] = {L.x, L.y, L.z, L.w};
+              const float lv[4] = {L.x, L.y, L.z, L.w};  // minus the row statistic
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int cc = g * 4 + e;
                 float x;
                 if constexpr (kMode == 2) {
-                  x = fmaf(s[cc], scale, fmaf(lg2(noise[cc]), -p.inv_tau, -lv[e]));
+                  x = fmaf(s[cc], scale, fmaf(lg2(noise[cc]), -p.inv_tau, lv[e]));
                 } else if constexpr (kMode == 3) {
                   const float l2 = seeded_lg2_exp_rand(static_cast<uint32_t>(q_base + ch * 32 + cc),
                                                        static_cast<uint32_t>(key), head_key);
-                  x = fmaf(s[cc], scale, fmaf(l2, -p.inv_tau, -lv[e]));
+                  x = fmaf(s[cc], scale, fmaf(l2, -p.inv_tau, lv[e]));
                 } else {
                   x = 0.f;  // (modes 0, 1, 4 take the packed path below)
                 }
@@ -346,12 +424,28 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
               if constexpr (kMode != 2 && kMode != 3) {
                 // two logits per FMA instruction (packed f32x2 of sm_100)
                 const float2 sc2 = make_float2(scale, scale);
-                const float2 x01 = __ffma2_rn(make_float2(s[g * 4 + 0], s[g * 4 + 1]), sc2, make_float2(-lv[0], -lv[1]));
-                const float2 x23 = __ffma2_rn(make_float2(s[g * 4 + 2], s[g * 4 + 3]), sc2, make_float2(-lv[2], -lv[3]));
-                s[g * 4 + 0] = ex2(x01.x);
-                s[g * 4 + 1] = ex2(x01.y);
-                s[g * 4 + 2] = ex2(x23.x);
-                s[g * 4 + 3] = ex2(x23.y);
+                const float2 x01 = __ffma2_rn(make_float2(s[g * 4 + 0], s[g * 4 + 1]), sc2, make_float2(lv[0], lv[1]));
+                const float2 x23 = __ffma2_rn(make_float2(s[g * 4 + 2], s[g * 4 + 3]), sc2, make_float2(lv[2], lv[3]));
+                // pairs alternate between the MUFU and the FMA pipe in the configured proportion
+                constexpr int kQ = ASUKA_COL_POLY_QUARTERS;
+                const bool poly01b = kQ == 3 && (g & 1) != 0;
+                const bool poly23 = kQ >= 2 || (kQ == 1 && (g & 1) != 0);
+                if (poly01b) {
+                  const float2 e01 = ex2_fma_pipe(x01);
+                  s[g * 4 + 0] = e01.x;
+                  s[g * 4 + 1] = e01.y;
+                } else {
+                  s[g * 4 + 0] = ex2(x01.x);
+                  s[g * 4 + 1] = ex2(x01.y);
+                }
+                if (poly23) {
+                  const float2 e23 = ex2_fma_pipe(x23);
+                  s[g * 4 + 2] = e23.x;
+                  s[g * 4 + 3] = e23.y;
+                } else {
+                  s[g * 4 + 2] = ex2(x23.x);
+                  s[g * 4 + 3] = ex2(x23.y);
+                }
               }
             }
             if (tile_has_mask) {
@@ -686,6 +780,7 @@ ColParams make_params(const ScoreArgs& a, const AttnShape& s) {
   p.er_sq = a.er_stride_q;
   p.seed = a.seed;
   p.status = device_status_words();
+  p.chained = a.chained;
   return p;
 }
 
@@ -704,9 +799,9 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
   else kern = s.bf16 ? col_scores_kernel<true, 3> : col_scores_kernel<false, 3>;
   cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (e != cudaSuccess) return e;
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, p);
+  e = launch_dependent(kern, grid, dim3(kThreads), kSmemBytes, stream, mq, mk, p);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 namespace asuka {
 
 // Device-side record of bounded waits that expired: word 0 = count, word 1 = last site id.
@@ -15,6 +17,24 @@ void count_launch();
 cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 // error unless the registers the kernel's roles ask for after setmaxnreg fit in what the CTA gets at launch
 cudaError_t check_register_budget(const void* kernel, int threads, int regs_wanted_total);
+
+// Launch with the programmatic-stream-serialization attribute: the kernel may be scheduled while
+// the one ahead of it in the stream drains; it orders itself with griddepcontrol.wait.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 struct AttnShape {
   int B, H, Sq, Skv;  // H: query heads
@@ -40,6 +60,8 @@ struct ScoreArgs {
   float tau;
   uint64_t seed;
   int mode;                // asuka_score_mode
+  int chained;             // 1: the kernel ahead in the stream is this library's own and writes none of
+                           // q and k, so the K tiles may be fetched before that kernel has finished
 };
 cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
                               const AttnShape& s, cudaStream_t stream);

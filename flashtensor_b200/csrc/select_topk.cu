@@ -14,6 +14,7 @@
 // integer work on exact keys, so the result is deterministic.
 #include "../../include/asuka_b200.h"
 #include "kernels.h"
+#include "sm100_ptx.cuh"
 
 namespace asuka {
 namespace {
@@ -68,6 +69,9 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const SelectArgs
   int32_t* out = a.idx + static_cast<size_t>(row) * n_out;
   const int ncand = a.mode == ASUKA_SELECT_TOPK_RECENT ? a.S - a.recent : a.S;
 
+  // (launched as a programmatic dependent: the scores are the output of the kernel ahead)
+  sm100::griddep_wait();
+  sm100::griddep_launch_dependents();
   for (int j = tid; j < ncand; j += kSelThreads) keys[j] = make_key<KeyT>(a, srow, qrow, j);
   hist[tid] = 0;
   hist[tid + kSelThreads] = 0;
@@ -203,14 +207,14 @@ cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream) {
   if (wide) {
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(select_kernel<uint64_t>), static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    select_kernel<uint64_t><<<a.rows, kSelThreads, smem, stream>>>(a);
+    e = launch_dependent(select_kernel<uint64_t>, dim3(a.rows), dim3(kSelThreads), smem, stream, a);
   } else {
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(select_kernel<uint32_t>), static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    select_kernel<uint32_t><<<a.rows, kSelThreads, smem, stream>>>(a);
+    e = launch_dependent(select_kernel<uint32_t>, dim3(a.rows), dim3(kSelThreads), smem, stream, a);
   }
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace asuka

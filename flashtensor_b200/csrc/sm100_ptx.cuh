@@ -96,6 +96,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may begin before the kernel ahead of it in the stream has finished; everything it
+// reads from, or writes over, that kernel's data has to come after griddep_wait(), which returns
+// once the earlier grids have completed and their memory operations are visible.  Without the
+// attribute both instructions do nothing.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// lets the next kernel in the stream be scheduled as soon as every CTA of this grid has said so
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), always CTA-local, never multicast
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
