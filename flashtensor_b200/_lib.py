@@ -29,14 +29,15 @@ class Tensor(ctypes.Structure):
 class AttnParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor), ("lse", Tensor),
               ("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32),
-              ("softcap", ctypes.c_float)]
+              ("softcap", ctypes.c_float), ("workspace", ctypes.c_void_p),
+              ("workspace_bytes", ctypes.c_uint64)]
 
 
 class ScoreParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("lse", Tensor), ("score", Tensor), ("score_sq", Tensor),
               ("exp_rand", Tensor), ("softmax_scale", ctypes.c_float), ("tau", ctypes.c_float),
               ("seed", ctypes.c_uint64), ("causal", ctypes.c_int32), ("mode", ctypes.c_int32),
-              ("corm_mask", Tensor)]
+              ("corm_mask", Tensor), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64)]
 
 
 class SelectParams(ctypes.Structure):
@@ -78,7 +79,9 @@ SYMBOLS = {
     "asuka_b200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "asuka_b200_launch_count": (ctypes.c_uint64, []),
     "asuka_b200_attn_fwd": (ctypes.c_int, [ctypes.POINTER(AttnParams), ctypes.c_void_p]),
+    "asuka_b200_attn_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(AttnParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_col_scores": (ctypes.c_int, [ctypes.POINTER(ScoreParams), ctypes.c_void_p]),
+    "asuka_b200_col_scores_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(ScoreParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_keyformer_rowstat": (ctypes.c_int, [ctypes.POINTER(ScoreParams), ctypes.c_void_p]),
     "asuka_b200_select_topk": (ctypes.c_int, [ctypes.POINTER(SelectParams), ctypes.c_void_p]),
     "asuka_b200_pool_scores": (ctypes.c_int, [ctypes.POINTER(Tensor), ctypes.POINTER(Tensor), ctypes.c_int32, ctypes.c_void_p]),
@@ -88,6 +91,7 @@ SYMBOLS = {
     "asuka_b200_ea_fwd": (ctypes.c_int, [ctypes.POINTER(SimaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_linattn32_fwd": (ctypes.c_int, [ctypes.POINTER(LinAttn32Params), ctypes.c_void_p]),
     "asuka_b200_case_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.POINTER(ctypes.c_size_t)]),
+    "asuka_b200_case_workspace_bytes_split": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_h2o": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "asuka_b200_h2o_static": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.c_void_p]),
     "asuka_b200_roco": (ctypes.c_int, [ctypes.POINTER(CaseParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),

@@ -23,6 +23,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "kernels.h"
 #include "sm100_ptx.cuh"
 
@@ -54,6 +56,13 @@ struct FwdParams {
   void* out;                 // [B, Sq, H, 128], 16-bit, strides in elements
   int64_t o_sb, o_ss, o_sh;
   uint32_t* status;
+  // Key-range split, for launches with fewer work items than SMs can share evenly: the keys of
+  // every item are dealt out to `parts` items of `ceil(n / parts)` key tiles each.  A query tile
+  // served by more than one part leaves, per part, its unnormalised O (f32), its exponent
+  // reference and its row sum in the workspace; attn_merge_kernel combines them in part order.
+  int parts;
+  float* part_o;             // [B*H, Sq, parts, 128]
+  float* part_ml;            // [B*H, Sq, parts, 2]
 };
 
 struct Bars {
@@ -107,41 +116,82 @@ __device__ __forceinline__ void record_timeout(uint32_t* status, uint32_t site) 
 }
 
 // number of 128-key tiles query tile [q0, q0+128) has to visit
-__device__ __forceinline__ int kv_tiles_for(int q0, const FwdParams& p) {
+__host__ __device__ __forceinline__ int kv_tiles_for(int q0, const FwdParams& p) {
   if (q0 >= p.Sq) return 0;
   int last = p.Skv - 1;
   if (p.causal) {
-    int qlast = min(q0 + kTile - 1, p.Sq - 1);
-    last = min(last, qlast + p.diag_off);
+    const int qlast = q0 + kTile - 1 < p.Sq - 1 ? q0 + kTile - 1 : p.Sq - 1;
+    last = last < qlast + p.diag_off ? last : qlast + p.diag_off;
   }
   return last / kTile + 1;
 }
 
+
 // One work item: 256 query rows of one (batch, head).
 struct Item {
   int b, h;
-  int q0[2];    // first row of each 128-row tile
-  int n_kv[2];  // 128-key tiles each tile visits (0: the tile lies past the end of the sequence)
+  int q0[2];      // first row of each 128-row tile
+  int j0;         // first key tile of this item (0 unless the keys are split)
+  int n_kv[2];    // 128-key tiles each tile visits from j0 on (0: nothing for this tile in this item)
   int n_max;
+  int part;       // which part of the key range this item is
+  int nparts[2];  // parts that serve each tile (1: this item writes the tile's final result)
 };
 
-// The it-th item of this CTA.  Items are sorted heaviest first; wave w of gridDim.x items is dealt
-// out forwards when w is even and backwards when it is odd, which evens out the totals.
+// Item `idx` of the launch; items are numbered heaviest first.  kSplit = false is the common case
+// of one item per 256-row block, compiled without any of the key-range arithmetic (which costs
+// the softmax warps registers they do not have).
+template <bool kSplit>
+__device__ __forceinline__ void decode_item(int idx, const FwdParams& p, Item* item) {
+  const int bh_count = p.B * p.H;
+  if constexpr (!kSplit) {
+    const int qb = p.nq_blocks - 1 - idx / bh_count;
+    const int bh = idx % bh_count;
+    item->b = bh / p.H;
+    item->h = bh % p.H;
+    item->q0[0] = qb * 2 * kTile;
+    item->q0[1] = qb * 2 * kTile + kTile;
+    item->j0 = 0;
+    item->n_kv[0] = kv_tiles_for(item->q0[0], p);
+    item->n_kv[1] = kv_tiles_for(item->q0[1], p);
+    item->n_max = max(item->n_kv[0], item->n_kv[1]);
+    item->part = 0;
+    item->nparts[0] = item->nparts[1] = 1;
+    return;
+  }
+  const int per_block = bh_count * p.parts;
+  const int qb = p.nq_blocks - 1 - idx / per_block;
+  const int rem = idx % per_block;
+  const int bh = rem % bh_count;
+  item->part = rem / bh_count;
+  item->b = bh / p.H;
+  item->h = bh % p.H;
+  item->q0[0] = qb * 2 * kTile;
+  item->q0[1] = qb * 2 * kTile + kTile;
+  const int full0 = kv_tiles_for(item->q0[0], p), full1 = kv_tiles_for(item->q0[1], p);
+  const int full = full0 > full1 ? full0 : full1;
+  const int len = (full + p.parts - 1) / p.parts;  // key tiles per part (>= 1)
+  item->j0 = item->part * len;
+  const int r0 = full0 - item->j0 < len ? full0 - item->j0 : len;
+  const int r1 = full1 - item->j0 < len ? full1 - item->j0 : len;
+  item->n_kv[0] = r0 > 0 ? r0 : 0;
+  item->n_kv[1] = r1 > 0 ? r1 : 0;
+  item->n_max = item->n_kv[0] > item->n_kv[1] ? item->n_kv[0] : item->n_kv[1];
+  item->nparts[0] = (full0 + len - 1) / len;
+  item->nparts[1] = (full1 + len - 1) / len;
+}
+
+// The it-th item of this CTA: wave w of gridDim.x items is dealt out forwards when w is even and
+// backwards when it is odd, which evens out the totals (at 32 heads and S = 4096 the busiest CTA
+// gets 3 % more than the mean; assigning longest-first to the least-loaded CTA on the host would
+// get within 2.5 %, the items being as coarse as they are, and was not worth a table).
+template <bool kSplit>
 __device__ __forceinline__ bool get_item(int it, const FwdParams& p, Item* item) {
   const int G = static_cast<int>(gridDim.x);
   const int r = static_cast<int>(blockIdx.x);
   const int idx = it * G + ((it & 1) ? G - 1 - r : r);
   if (idx >= p.n_items) return false;
-  const int bh_count = p.B * p.H;
-  const int qb = p.nq_blocks - 1 - idx / bh_count;
-  const int bh = idx % bh_count;
-  item->b = bh / p.H;
-  item->h = bh % p.H;
-  item->q0[0] = qb * 2 * kTile;
-  item->q0[1] = qb * 2 * kTile + kTile;
-  item->n_kv[0] = kv_tiles_for(item->q0[0], p);
-  item->n_kv[1] = kv_tiles_for(item->q0[1], p);
-  item->n_max = max(item->n_kv[0], item->n_kv[1]);
+  decode_item<kSplit>(idx, p, item);
   return true;
 }
 // with an odd number of waves the last, backwards-dealt wave can skip a CTA that still has none
@@ -151,7 +201,7 @@ __device__ __forceinline__ int item_waves(const FwdParams& p) {
 
 // kCap: Gemma-2 style soft-capping, logits -> cap * tanh(logits / cap) before the mask
 // (cases/kernels/gemma2.py:30-33; the reference emits tanh.approx.f32 too, to_triton.cpp:351-369).
-template <bool kBF16, bool kCap>
+template <bool kBF16, bool kCap, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
@@ -223,7 +273,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t qn[2] = {0, 0};    // items in which tile t was loaded so far
       Item it_;
       for (int it = 0; it < n_waves && ok; ++it) {
-        if (!get_item(it, p, &it_)) continue;
+        if (!get_item<kSplit>(it, p, &it_)) continue;
         for (int t = 0; t < 2 && ok; ++t) {
           if (it_.n_kv[t] == 0) continue;
           if (qn[t] > 0) {  // the previous item's last QK^T of this tile must have read Q_t
@@ -245,8 +295,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           const uint32_t bar = smem_u32(&bars.k_full[st]);
           mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, it_.h / p.group, j * kTile, it_.b);
-          tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, it_.h / p.group, j * kTile, it_.b);
+          tma_load_4d(sK + st * kTileBytes, &map_k, bar, 0, it_.h / p.group, ((kSplit ? it_.j0 : 0) + j) * kTile, it_.b);
+          tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, bar, 64, it_.h / p.group, ((kSplit ? it_.j0 : 0) + j) * kTile, it_.b);
         }
       }
       if (!ok) {
@@ -264,7 +314,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t vc = 0;
       Item it_;
       for (int it = 0; it < n_waves && ok; ++it) {
-        if (!get_item(it, p, &it_)) continue;
+        if (!get_item<kSplit>(it, p, &it_)) continue;
         for (int j = 0; j < it_.n_max && ok; ++j, ++vc) {
           const int st = vc % kVStages;
           const uint32_t use = vc / kVStages;
@@ -274,8 +324,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           const uint32_t bar = smem_u32(&bars.v_full[st]);
           mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, it_.h / p.group, j * kTile, it_.b);
-          tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, it_.h / p.group, j * kTile, it_.b);
+          tma_load_4d(sV + st * kTileBytes, &map_v, bar, 0, it_.h / p.group, ((kSplit ? it_.j0 : 0) + j) * kTile, it_.b);
+          tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, bar, 64, it_.h / p.group, ((kSplit ? it_.j0 : 0) + j) * kTile, it_.b);
         }
       }
       if (!ok) {
@@ -308,7 +358,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t on[2] = {0, 0};      // items of tile t before this one (parity of q_full, o_free)
       Item it_;
       for (int it = 0; it < n_waves && ok; ++it) {
-        if (!get_item(it, p, &it_)) continue;
+        if (!get_item<kSplit>(it, p, &it_)) continue;
         const int n_max = it_.n_max;
         for (int t = 0; t < 2 && ok; ++t) {
           if (it_.n_kv[t] > 0) ok = wait_all(&bars.q_full[t], on[t] & 1, 3);
@@ -398,7 +448,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint32_t on = 0;  // items of this tile before the current one
     Item it_;
     for (int it = 0; it < n_waves && ok; ++it) {
-      if (!get_item(it, p, &it_)) continue;
+      if (!get_item<kSplit>(it, p, &it_)) continue;
       const int n_t = it_.n_kv[t];
       if (n_t == 0) continue;
       const int row = it_.q0[t] + r_in_tile;
@@ -413,8 +463,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[t]), (sn + j) & 1, abortp));
         if (!ok) { if (lane == 0) record_timeout(p.status, 7); break; }
         tc_fence_after_sync();
-        const bool masked_tile = j * kTile + kTile - 1 > tile_min_lim;
-        const int thr = lim - j * kTile;  // columns > thr of this tile are masked for this row
+        const int jk = ((kSplit ? it_.j0 : 0) + j) * kTile;  // first key of this tile
+        const bool masked_tile = jk + kTile - 1 > tile_min_lim;
+        const int thr = lim - jk;  // columns > thr of this tile are masked for this row
 
         // The whole 128-wide row is exponentiated at once against the reference left by earlier
         // tiles, so the MUFU starts right after the TMEM load and runs without a gap; the tile's
@@ -439,6 +490,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 128; ++i) e[i] = (i > thr) ? -INFINITY : e[i];
         }
+#ifndef ASUKA_NO_SEED
         if (j == 0) {
           // the first tile of an item has no reference yet: take the tile's true row maximum (the
           // capped and scaled logit is monotone in the raw one) instead of exponentiating blind
@@ -453,17 +505,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
           m_ref = mx > -INFINITY ? mx * (kCap ? p.cap_out : scale) : 0.f;
         }
+#endif
         {
           // two logits per FMA instruction (packed f32x2): the softmax warp of a tile runs alone on
           // its scheduler and is bound by the number of instructions it has to issue
           const float mul = kCap ? p.cap_out : scale;
           const float2 mul2 = make_float2(mul, mul), neg_m2 = make_float2(-m_ref, -m_ref);
+#ifdef ASUKA_NO_PACKED
+          (void)mul2; (void)neg_m2;
+#pragma unroll
+          for (int i = 0; i < 128; ++i) e[i] = ex2(fmaf(e[i], mul, -m_ref));
+#else
 #pragma unroll
           for (int i = 0; i < 64; ++i) {
             const float2 x = __ffma2_rn(make_float2(e[2 * i], e[2 * i + 1]), mul2, neg_m2);
             e[2 * i] = ex2(x.x);
             e[2 * i + 1] = ex2(x.y);
           }
+#endif
         }
         // The tile's row sum doubles as the overflow probe: it bounds every term from above, and it
         // is NaN or infinite exactly when some term is.  P is packed
@@ -552,7 +611,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.o_done[t]), on & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 9); break; }
       tc_fence_after_sync();
-      {
+#ifdef ASUKA_REDECODE
+      get_item<kSplit>(it, p, &it_);  // (decoded again rather than kept in registers across the key loop)
+#endif
+      if (kSplit && it_.nparts[t] > 1) {
+        // this tile's keys are shared with other items: leave the unnormalised O, the exponent
+        // reference and the row sum for the merge (a row that saw no key in this part has l = 0
+        // and must not set the scale: its reference goes out as -inf)
+        const size_t prow = ((static_cast<size_t>(it_.b) * p.H + it_.h) * p.Sq + row) * p.parts + it_.part;
+        float* orow = p.part_o + prow * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
+          tmem_wait_ld();
+          if (c == 3) {
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars.o_free[t]));
+          }
+          if (row < p.Sq) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 4) = make_uint4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+          }
+        }
+        if (row < p.Sq)
+          *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(l > 0.f ? m_ref : -INFINITY, l);
+      } else {
         const float inv_l = 1.f / l;
         uint16_t* orow = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(it_.b) * p.o_sb +
                          static_cast<int64_t>(row) * p.o_ss + static_cast<int64_t>(it_.h) * p.o_sh;
@@ -595,11 +680,97 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
+// Combines the parts of a key-range split.  One warp per query row, lane = four output columns:
+// every part's reference, row sum and 512-byte O row are read (they were written moments ago and
+// sit in L2) with all loads of a row in flight at once, scaled to the common reference and added
+// in part order, so the result does not depend on which part finished first.
+constexpr int kMaxParts = 8;
+constexpr int kMergeRows = 8;  // rows (= warps) per CTA
+template <bool kBF16>
+__global__ void __launch_bounds__(kMergeRows * 32) attn_merge_kernel(const FwdParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh_count = p.B * p.H;
+  const int rb = static_cast<int>(blockIdx.x) / bh_count;  // block of kMergeRows query rows
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int b = bh / p.H, h = bh % p.H;
+  const int row = rb * kMergeRows + warp;
+  const int q0 = (row / kTile) * kTile;
+  // the same arithmetic as get_item: the parts of the 256-row block this row's tile belongs to
+  const int qa = (row / (2 * kTile)) * 2 * kTile;
+  const int len = (max(kv_tiles_for(qa, p), kv_tiles_for(qa + kTile, p)) + p.parts - 1) / p.parts;
+  const int nparts = (kv_tiles_for(q0, p) + len - 1) / len;
+  griddep_wait();               // the parts are the output of the kernel ahead
+  griddep_launch_dependents();
+  if (nparts <= 1 || row >= p.Sq) return;  // (one part: the forward kernel wrote the result itself)
+  const size_t prow = (static_cast<size_t>(bh) * p.Sq + row) * p.parts;
+  float2 ml[kMaxParts];
+  float4 o[kMaxParts];
+#pragma unroll
+  for (int q = 0; q < kMaxParts; ++q) {
+    if (q < nparts) {
+      ml[q] = *reinterpret_cast<const float2*>(p.part_ml + (prow + q) * 2);
+      o[q] = *reinterpret_cast<const float4*>(p.part_o + (prow + q) * 128 + lane * 4);
+    }
+  }
+  float m = -INFINITY;
+#pragma unroll
+  for (int q = 0; q < kMaxParts; ++q)
+    if (q < nparts) m = fmaxf(m, ml[q].x);
+  float l = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int q = 0; q < kMaxParts; ++q) {
+    if (q < nparts) {
+      const float w = ml[q].x > -INFINITY ? ex2(ml[q].x - m) : 0.f;
+      l = fmaf(w, ml[q].y, l);
+      acc.x = fmaf(w, o[q].x, acc.x);
+      acc.y = fmaf(w, o[q].y, acc.y);
+      acc.z = fmaf(w, o[q].z, acc.z);
+      acc.w = fmaf(w, o[q].w, acc.w);
+    }
+  }
+  const float inv_l = 1.f / l;
+  uint16_t* orow = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(b) * p.o_sb +
+                   static_cast<int64_t>(row) * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
+  uint2 v;
+  v.x = pack2<kBF16>(acc.x * inv_l, acc.y * inv_l);
+  v.y = pack2<kBF16>(acc.z * inv_l, acc.w * inv_l);
+  *reinterpret_cast<uint2*>(orow + lane * 4) = v;
+  if (p.lse2 != nullptr && lane == 0) p.lse2[static_cast<size_t>(bh) * p.Sq + row] = m + log2f(l);
+}
+
 }  // namespace
+
+// How many parts the key range of every work item is cut into.  Splitting pays only when the
+// launch has fewer items than SMs and the items are long (measured at head counts of 4 to 32 and
+// S = 1024 to 4096: the partial results cost about as much L2 traffic again as the inputs); it
+// needs workspace for the parts' partial results.
+int attn_fwd_parts(const AttnShape& s, int num_sms, size_t ws_bytes) {
+  const long long nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
+  const long long n_items = nq_blocks * s.B * s.H;
+  const int max_tiles = (s.Skv + kTile - 1) / kTile;
+  int parts = 1;
+#ifdef ASUKA_TUNE_ENV
+  if (const char* e = getenv("ASUKA_FWD_PARTS")) {
+    parts = atoi(e);
+    while (parts > 1 && attn_fwd_split_bytes(s, parts) > ws_bytes) parts /= 2;
+    return parts;
+  }
+#endif
+  if (n_items < num_sms && max_tiles >= 32) parts = 2 * n_items <= num_sms ? 4 : 2;
+  while (parts > 1 && attn_fwd_split_bytes(s, parts) > ws_bytes) parts /= 2;
+  return parts;
+}
+
+size_t attn_fwd_split_bytes(const AttnShape& s, int parts) {
+  if (parts <= 1) return 0;
+  const size_t rows = static_cast<size_t>(s.B) * s.H * s.Sq;
+  return rows * parts * (128 + 2) * sizeof(float);
+}
 
 cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                             void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, float* lse2,
-                            const AttnShape& s, int num_sms, cudaStream_t stream) {
+                            const AttnShape& s, int num_sms, void* split_ws, int parts, cudaStream_t stream) {
   FwdParams p;
   p.B = s.B;
   p.H = s.H;
@@ -608,7 +779,8 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.causal = s.causal;
   p.diag_off = s.Skv - s.Sq;
   p.nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
-  p.n_items = p.nq_blocks * s.B * s.H;
+  p.parts = parts > 1 && split_ws != nullptr ? parts : 1;
+  p.n_items = p.nq_blocks * s.B * s.H * p.parts;
   p.group = s.group;
   p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
   p.cap_in = s.softcap > 0.f ? s.softmax_scale / s.softcap : 0.f;
@@ -619,15 +791,27 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.o_ss = o_ss;
   p.o_sh = o_sh;
   p.status = device_status_words();
+  p.part_o = static_cast<float*>(split_ws);
+  p.part_ml = p.part_o + static_cast<size_t>(s.B) * s.H * s.Sq * p.parts * 128;
   const dim3 grid(static_cast<unsigned>(p.n_items < num_sms ? p.n_items : num_sms));
   void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, FwdParams);
-  if (s.softcap > 0.f) kern = s.bf16 ? attn_fwd_kernel<true, true> : attn_fwd_kernel<false, true>;
-  else kern = s.bf16 ? attn_fwd_kernel<true, false> : attn_fwd_kernel<false, false>;
+  if (p.parts > 1) {
+    if (s.softcap > 0.f) kern = s.bf16 ? attn_fwd_kernel<true, true, true> : attn_fwd_kernel<false, true, true>;
+    else kern = s.bf16 ? attn_fwd_kernel<true, false, true> : attn_fwd_kernel<false, false, true>;
+  } else {
+    if (s.softcap > 0.f) kern = s.bf16 ? attn_fwd_kernel<true, true, false> : attn_fwd_kernel<false, true, false>;
+    else kern = s.bf16 ? attn_fwd_kernel<true, false, false> : attn_fwd_kernel<false, false, false>;
+  }
   cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (e != cudaSuccess) return e;
   e = check_register_budget(reinterpret_cast<const void*>(kern), kThreads, 128 * kUtilRegs + 256 * kSoftmaxRegs);
   if (e != cudaSuccess) return e;
   e = launch_dependent(kern, grid, dim3(kThreads), kSmemBytes, stream, mq, mk, mv, p);
+  count_launch();
+  if (e != cudaSuccess || p.parts == 1) return e;
+  const dim3 mgrid(static_cast<unsigned>((s.Sq + kMergeRows - 1) / kMergeRows) * s.B * s.H);
+  e = launch_dependent(s.bf16 ? attn_merge_kernel<true> : attn_merge_kernel<false>, mgrid, dim3(kMergeRows * 32), 0,
+                       stream, p);
   count_launch();
   return e;
 }

@@ -184,7 +184,20 @@ int check_qk(const asuka_tensor& q, const asuka_tensor& k, float scale, int caus
 
 int map_cuda(cudaError_t e) { return e == cudaSuccess ? ASUKA_OK : ASUKA_ERR_CUDA; }
 
-int attn_fwd_impl(const asuka_attn_params* p, float* lse_override, cudaStream_t stream) {
+// 256-byte aligned start of the usable part of an optional scratch area, and its size
+void* align_ws(void* ws, size_t bytes, size_t* usable) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(ws);
+  const uintptr_t up = (a + 255u) & ~static_cast<uintptr_t>(255u);
+  if (ws == nullptr || up - a >= bytes) {
+    *usable = 0;
+    return nullptr;
+  }
+  *usable = bytes - (up - a);
+  return reinterpret_cast<void*>(up);
+}
+
+int attn_fwd_impl(const asuka_attn_params* p, float* lse_override, cudaStream_t stream, void* ws = nullptr,
+                  size_t ws_bytes = 0) {
   if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
   QKV c;
   int r;
@@ -207,8 +220,11 @@ int attn_fwd_impl(const asuka_attn_params* p, float* lse_override, cudaStream_t 
   if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k)) || (r = make_map(&mv, p->v))) return r;
   const int sms = sm_count();
   if (sms <= 0) return ASUKA_ERR_CUDA;
+  size_t usable = 0;
+  void* split_ws = align_ws(ws != nullptr ? ws : p->workspace, ws != nullptr ? ws_bytes : p->workspace_bytes, &usable);
+  const int parts = attn_fwd_parts(c.s, sms, usable);
   return map_cuda(launch_attn_fwd(mq, mk, mv, p->out.ptr, p->out.stride[0], p->out.stride[1],
-                                  p->out.stride[2], lse, c.s, sms, stream));
+                                  p->out.stride[2], lse, c.s, sms, split_ws, parts, stream));
 }
 
 
@@ -280,7 +296,8 @@ int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a)
 }
 
 // `chained`: the kernel ahead in the stream is one of this library's that writes neither q nor k
-int col_scores_impl(const asuka_score_params* p, cudaStream_t stream, bool chained = false) {
+int col_scores_impl(const asuka_score_params* p, cudaStream_t stream, bool chained = false, void* ws = nullptr,
+                    size_t ws_bytes = 0) {
   QKV c;
   ScoreArgs a;
   int r = prep_scores(p, false, &c, &a);
@@ -288,7 +305,12 @@ int col_scores_impl(const asuka_score_params* p, cudaStream_t stream, bool chain
   a.chained = chained ? 1 : 0;
   CUtensorMap mq, mk;
   if ((r = make_map(&mq, p->q)) || (r = make_map(&mk, p->k))) return r;
-  return map_cuda(launch_col_scores(mq, mk, a, c.s, stream));
+  const int sms = sm_count();
+  if (sms <= 0) return ASUKA_ERR_CUDA;
+  size_t usable = 0;
+  void* split_ws = align_ws(ws != nullptr ? ws : p->workspace, ws != nullptr ? ws_bytes : p->workspace_bytes, &usable);
+  const int chunks = col_scores_chunks(c.s, a.mode, sms, usable);
+  return map_cuda(launch_col_scores(mq, mk, a, c.s, split_ws, chunks, stream));
 }
 
 int kf_rowstat_impl(const asuka_score_params* p, cudaStream_t stream) {
@@ -417,6 +439,23 @@ size_t case_ws_bytes(const asuka_case_params* p) {
   return bytes;
 }
 
+// what the split of work items would like on top of case_ws_bytes on the current device
+size_t case_split_bytes(const asuka_case_params* p, CaseKind kind) {
+  if (p->k.ndim != 4 || p->q.ndim != 4) return 0;
+  const int sms = sm_count();
+  if (sms <= 0) return 0;
+  AttnShape s;
+  std::memset(&s, 0, sizeof(s));
+  s.B = static_cast<int>(p->q.shape[0]);
+  s.Sq = static_cast<int>(p->q.shape[1]);
+  s.H = static_cast<int>(p->q.shape[2]);
+  s.Skv = static_cast<int>(p->k.shape[1]);
+  const int mode = kind == CASE_H2O ? ASUKA_SCORE_SUM : kind == CASE_ROCO ? ASUKA_SCORE_SUM_SQ : ASUKA_SCORE_PERTURBED;
+  const size_t fwd = attn_fwd_split_bytes(s, attn_fwd_parts(s, sms, ~static_cast<size_t>(0)));
+  const size_t col = col_scores_split_bytes(s, mode, col_scores_chunks(s, mode, sms, ~static_cast<size_t>(0)));
+  return ((col + 255) / 256) * 256 + fwd + 256;
+}
+
 int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_bytes,
               cudaStream_t stream) {
   if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
@@ -518,12 +557,36 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
     if (gqa && B * Hkv > 65535) return ASUKA_ERR_TOO_LARGE;
   }
 
-  int r = attn_fwd_impl(&fp, nullptr, stream);
+  // whatever the caller gave beyond the required part lets the kernels split their work items:
+  // first the column pass's partial sums (small), then the forward kernel's partial outputs
+  uint8_t* extra = static_cast<uint8_t*>(ws) + case_ws_bytes(p);
+  size_t extra_bytes = ws_bytes - case_ws_bytes(p);
+  void* col_ws = nullptr;
+  size_t col_bytes = 0;
+  {
+    QKV c; ScoreArgs a;
+    if (prep_scores(&sp, false, &c, &a) == ASUKA_OK) {
+      const int sms = sm_count();
+      size_t usable = 0;
+      void* base = align_ws(extra, extra_bytes, &usable);
+      if (sms > 0 && base != nullptr) {
+        const size_t want = col_scores_split_bytes(c.s, a.mode, col_scores_chunks(c.s, a.mode, sms, usable));
+        if (want > 0) {
+          col_ws = base;
+          col_bytes = want;
+          const size_t step = ((want + 255) / 256) * 256;
+          extra = static_cast<uint8_t*>(base) + step;
+          extra_bytes = usable > step ? usable - step : 0;
+        }
+      }
+    }
+  }
+  int r = attn_fwd_impl(&fp, nullptr, stream, extra_bytes > 0 ? extra : nullptr, extra_bytes);
   if (r != ASUKA_OK) return r;
   if (kind == CASE_KF) {
     if ((r = kf_rowstat_impl(&sp, stream)) != ASUKA_OK) return r;
   }
-  if ((r = col_scores_impl(&sp, stream, true)) != ASUKA_OK) return r;
+  if ((r = col_scores_impl(&sp, stream, true, col_ws, col_bytes)) != ASUKA_OK) return r;
   if (gqa) {
     r = map_cuda(launch_group_mean(head_scores, static_cast<float*>(p->score.ptr), static_cast<int>(B * Hkv),
                                    static_cast<int>(H / Hkv), static_cast<int>(p->k.shape[1]), stream));
@@ -729,9 +792,41 @@ int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes) {
   return ASUKA_OK;
 }
 
+int asuka_b200_case_workspace_bytes_split(const asuka_case_params* p, size_t* bytes) {
+  const int r = asuka_b200_case_workspace_bytes(p, bytes);
+  // required part + what the work-item splits would like; RoCo's column pass asks most
+  if (r == ASUKA_OK) *bytes += case_split_bytes(p, CASE_ROCO);
+  return r;
+}
+
+int asuka_b200_attn_workspace_bytes(const asuka_attn_params* p, size_t* bytes) {
+  if (p == nullptr || bytes == nullptr) return ASUKA_ERR_NULL_POINTER;
+  QKV c;
+  int r = check_qk(p->q, p->k, p->softmax_scale, p->causal, &c);
+  if (r != ASUKA_OK) return r;
+  const int sms = sm_count();
+  if (sms <= 0) return ASUKA_ERR_CUDA;
+  const size_t n = attn_fwd_split_bytes(c.s, attn_fwd_parts(c.s, sms, ~static_cast<size_t>(0)));
+  *bytes = n > 0 ? n + 256 : 0;
+  return ASUKA_OK;
+}
+
+int asuka_b200_col_scores_workspace_bytes(const asuka_score_params* p, size_t* bytes) {
+  if (p == nullptr || bytes == nullptr) return ASUKA_ERR_NULL_POINTER;
+  QKV c;
+  int r = check_qk(p->q, p->k, p->softmax_scale, p->causal, &c);
+  if (r != ASUKA_OK) return r;
+  const int sms = sm_count();
+  if (sms <= 0) return ASUKA_ERR_CUDA;
+  const size_t n = col_scores_split_bytes(c.s, p->mode, col_scores_chunks(c.s, p->mode, sms, ~static_cast<size_t>(0)));
+  *bytes = n > 0 ? n + 256 : 0;
+  return ASUKA_OK;
+}
+
 int asuka_b200_h2o(const asuka_case_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
   return case_impl(p, CASE_H2O, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
+// (the static array is handed over as exactly the required size: no work-item splitting here)
 // H2O with the row statistic in the library's own fixed device array: no workspace argument, no
 // allocation.  The size check comes first, so an oversized request never reaches a launch.  The
 // first call on a device resolves the array's address (see h2o_static_scratch above).
@@ -749,7 +844,7 @@ int asuka_b200_h2o_static(const asuka_case_params* p, asuka_stream stream) {
   void* scratch = nullptr;
   r = h2o_static_scratch(&scratch);
   if (r != ASUKA_OK) return r;
-  return case_impl(p, CASE_H2O, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+  return case_impl(p, CASE_H2O, scratch, case_ws_bytes(p), static_cast<cudaStream_t>(stream));
 }
 int asuka_b200_roco(const asuka_case_params* p, void* ws, size_t ws_bytes, asuka_stream stream) {
   return case_impl(p, CASE_ROCO, ws, ws_bytes, static_cast<cudaStream_t>(stream));

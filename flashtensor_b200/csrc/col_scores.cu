@@ -24,6 +24,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "../../include/asuka_b200.h"
 #include "kernels.h"
 #include "sm100_ptx.cuh"
@@ -57,6 +59,13 @@ struct ColParams {
   uint64_t seed;
   uint32_t* status;
   int chained;        // the kernel ahead in the stream does not write q or k
+  // Query-range split, for launches with too few key blocks to fill the SMs: the query tiles are
+  // cut into `n_qchunks` ranges of `q_chunk` tiles, one CTA per (key block, range); every CTA
+  // leaves its partial sums in `part` ([n_qchunks, B*H, Skv], and `part_sq` alike) and
+  // sum_chunks_kernel adds them in range order.  n_qchunks = 1: no split, results go to `score`.
+  int q_chunk, n_qchunks;
+  float* part;
+  float* part_sq;
 };
 
 struct ColBars {
@@ -197,15 +206,20 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   volatile uint32_t* abortp = &abort_s;
 
   const int bh_count = p.B * p.H;
-  const int kvb = static_cast<int>(blockIdx.x) / bh_count;  // low key blocks are the long ones
+  const int blk = static_cast<int>(blockIdx.x) / bh_count;
+  const int kvb = blk / p.n_qchunks;  // low key blocks are the long ones
+  const int qc = p.n_qchunks - 1 - blk % p.n_qchunks;  // (late query ranges see the most keys)
   const int bh = static_cast<int>(blockIdx.x) % bh_count;
   const int b = bh / p.H, h = bh % p.H;
   const int kv0[2] = {kvb * 2 * kTile, kvb * 2 * kTile + kTile};
   const bool active[2] = {kv0[0] < p.Skv, kv0[1] < p.Skv};
-  // first query tile that can see the first key of each key tile
+  // this CTA's query tiles [i_lo, i_end), and the first of them that can see the first key of
+  // each key tile
+  const int i_lo = qc * p.q_chunk;
+  const int i_end = min(p.nq_tiles, i_lo + p.q_chunk);
   int i_start[2];
 #pragma unroll
-  for (int t = 0; t < 2; ++t) i_start[t] = p.causal ? max(0, kv0[t] - p.diag_off) / kTile : 0;
+  for (int t = 0; t < 2; ++t) i_start[t] = max(i_lo, p.causal ? max(0, kv0[t] - p.diag_off) / kTile : 0);
   const int i_begin = i_start[0];
   const int n_active = (active[0] ? 1 : 0) + (active[1] ? 1 : 0);
 
@@ -259,7 +273,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const float* lse_row = p.lse2 + (static_cast<size_t>(b) * p.H + h) * p.Sq;
     bool ok = true;
     if (p.chained) griddep_wait();  // the row statistic is the output of the kernel ahead
-    for (int i = i_begin; i < p.nq_tiles; ++i) {
+    for (int i = i_begin; i < i_end; ++i) {
       const int c = i - i_begin;
       const int st = c % kQStages;
       const uint32_t use = static_cast<uint32_t>(c / kQStages);
@@ -299,7 +313,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         return good;
       };
       bool ok = wait_all(&bars.k_full, 0, 22);
-      for (int i = i_begin; i < p.nq_tiles && ok; ++i) {
+      for (int i = i_begin; i < i_end && ok; ++i) {
         const int c = i - i_begin;
         const int st = c % kQStages;
         ok = wait_all(&bars.q_full[st], (c / kQStages) & 1, 23);
@@ -355,7 +369,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     bool hit = false;
 
     if (active[t]) {
-      for (int i = i_begin; i < p.nq_tiles; ++i) {
+      for (int i = i_begin; i < i_end; ++i) {
         const int c = i - i_begin;
         const int st = c % kQStages;
         if (i >= i_start[t]) {
@@ -387,7 +401,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
               }
               // the operand is read once, straight from HBM: pull the same chunk of the next query
               // tile into L2 now, so that its loads find it there one step later
-              if (i + 1 < p.nq_tiles) {
+              if (i + 1 < i_end) {
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                   const int qi = min(q_base + kTile + ch * 32 + e, p.Sq - 1);
@@ -502,12 +516,16 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (key < p.Skv) {  // (implies that this key tile is active)
       const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
       const float v = part_s[0][0][t][k_in_tile] + part_s[0][1][t][k_in_tile];
+      // with a query-range split the sums of this range go to its slab of the workspace (a range
+      // that sees none of the keys leaves zeros there)
+      const size_t slab = static_cast<size_t>(qc) * bh_count * p.Skv;
       if constexpr (kMode == 4) {
         reinterpret_cast<uint8_t*>(p.score)[o] = v != 0.f ? 1 : 0;
       } else {
-        p.score[o] = v;
+        (p.n_qchunks > 1 ? p.part + slab : p.score)[o] = v;
       }
-      if constexpr (kMode == 1) p.score_sq[o] = part_s[1][0][t][k_in_tile] + part_s[1][1][t][k_in_tile];
+      if constexpr (kMode == 1)
+        (p.n_qchunks > 1 ? p.part_sq + slab : p.score_sq)[o] = part_s[1][0][t][k_in_tile] + part_s[1][1][t][k_in_tile];
     }
   }
 }
@@ -754,6 +772,23 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
 }
 
+// Adds the partial sums of a query-range split in range order: out[i] = sum_c part[c][i].
+__global__ void __launch_bounds__(256) sum_chunks_kernel(const float* __restrict__ part, const float* __restrict__ part_sq,
+                                                         float* __restrict__ out, float* __restrict__ out_sq,
+                                                         int n_chunks, size_t n) {
+  griddep_wait();  // the partial sums are the output of the kernel ahead
+  griddep_launch_dependents();
+  const size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n) return;
+  float a = 0.f, q = 0.f;
+  for (int c = 0; c < n_chunks; ++c) {
+    a += part[c * n + i];
+    if (part_sq != nullptr) q += part_sq[c * n + i];
+  }
+  out[i] = a;
+  if (part_sq != nullptr) out_sq[i] = q;
+}
+
 ColParams make_params(const ScoreArgs& a, const AttnShape& s) {
   ColParams p;
   p.B = s.B;
@@ -781,16 +816,53 @@ ColParams make_params(const ScoreArgs& a, const AttnShape& s) {
   p.seed = a.seed;
   p.status = device_status_words();
   p.chained = a.chained;
+  p.q_chunk = p.nq_tiles;
+  p.n_qchunks = 1;
+  p.part = nullptr;
+  p.part_sq = nullptr;
   return p;
 }
 
 }  // namespace
 
+// Query ranges the column pass is worth cutting into on `num_sms` SMs (1: no split); every range
+// needs a [B*H, Skv] f32 slab of workspace per score tensor.
+int col_scores_chunks(const AttnShape& s, int mode, int num_sms, size_t ws_bytes) {
+  if (mode == ASUKA_SCORE_CORM) return 1;
+  const long long n_ctas = static_cast<long long>((s.Skv + 2 * kTile - 1) / (2 * kTile)) * s.B * s.H;
+  const int nq_tiles = (s.Sq + kTile - 1) / kTile;
+  int chunks = 1;
+#ifdef ASUKA_TUNE_ENV
+  if (const char* e = getenv("ASUKA_COL_CHUNKS")) {
+    chunks = atoi(e);
+    while (chunks > 1 && col_scores_split_bytes(s, mode, chunks) > ws_bytes) chunks /= 2;
+    return chunks;
+  }
+#endif
+  // measured at head counts of 4 to 32 and S = 1024 to 4096: worth it only for long query ranges
+  // and clearly fewer key blocks than the SMs can take in one wave and a bit
+  if (5 * n_ctas < 6LL * num_sms && nq_tiles >= 32) chunks = 2 * n_ctas <= num_sms ? 4 : 2;
+  while (chunks > 1 && col_scores_split_bytes(s, mode, chunks) > ws_bytes) chunks /= 2;
+  return chunks;
+}
+
+size_t col_scores_split_bytes(const AttnShape& s, int mode, int chunks) {
+  if (chunks <= 1) return 0;
+  const size_t slab = static_cast<size_t>(s.B) * s.H * s.Skv * sizeof(float);
+  return slab * chunks * (mode == ASUKA_SCORE_SUM_SQ ? 2 : 1);
+}
+
 cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
-                              const AttnShape& s, cudaStream_t stream) {
-  const ColParams p = make_params(a, s);
+                              const AttnShape& s, void* split_ws, int chunks, cudaStream_t stream) {
+  ColParams p = make_params(a, s);
+  if (chunks > 1 && split_ws != nullptr && a.mode != ASUKA_SCORE_CORM) {
+    p.q_chunk = (p.nq_tiles + chunks - 1) / chunks;
+    p.n_qchunks = (p.nq_tiles + p.q_chunk - 1) / p.q_chunk;
+    p.part = static_cast<float*>(split_ws);
+    p.part_sq = p.part + static_cast<size_t>(p.n_qchunks) * s.B * s.H * s.Skv;
+  }
   const int n_kvb = (s.Skv + 2 * kTile - 1) / (2 * kTile);
-  const dim3 grid(static_cast<unsigned>(n_kvb) * s.B * s.H);
+  const dim3 grid(static_cast<unsigned>(n_kvb) * p.n_qchunks * s.B * s.H);
   void (*kern)(CUtensorMap, CUtensorMap, ColParams) = nullptr;
   if (a.mode == ASUKA_SCORE_SUM) kern = s.bf16 ? col_scores_kernel<true, 0> : col_scores_kernel<false, 0>;
   else if (a.mode == ASUKA_SCORE_SUM_SQ) kern = s.bf16 ? col_scores_kernel<true, 1> : col_scores_kernel<false, 1>;
@@ -800,6 +872,13 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
   cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (e != cudaSuccess) return e;
   e = launch_dependent(kern, grid, dim3(kThreads), kSmemBytes, stream, mq, mk, p);
+  count_launch();
+  if (e != cudaSuccess || p.n_qchunks == 1) return e;
+  const size_t n = static_cast<size_t>(s.B) * s.H * s.Skv;
+  const bool sq = a.mode == ASUKA_SCORE_SUM_SQ;
+  e = launch_dependent(sum_chunks_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, stream,
+                       static_cast<const float*>(p.part), static_cast<const float*>(sq ? p.part_sq : nullptr),
+                       a.score, a.score_sq, p.n_qchunks, n);
   count_launch();
   return e;
 }

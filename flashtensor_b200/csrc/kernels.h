@@ -47,9 +47,14 @@ struct AttnShape {
 
 // q/k/v tensor maps: [B,S,H,128] boxes of 64 x 1 x 128 x 1, 128-byte swizzle.  `out` is written
 // with plain 16-byte stores (strides in elements).  `num_sms` sizes the persistent grid.
+// `split_ws` / `parts`: optional key-range split (see attn_fwd_parts); parts = 1 or a null
+// workspace runs every work item over its whole key range.
 cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                             void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, float* lse2,
-                            const AttnShape& s, int num_sms, cudaStream_t stream);
+                            const AttnShape& s, int num_sms, void* split_ws, int parts, cudaStream_t stream);
+// parts the key range is worth cutting into on `num_sms` SMs, limited by the workspace on offer
+int attn_fwd_parts(const AttnShape& s, int num_sms, size_t ws_bytes);
+size_t attn_fwd_split_bytes(const AttnShape& s, int parts);
 
 struct ScoreArgs {
   const float* lse2;       // [B,H,Sq]
@@ -63,8 +68,12 @@ struct ScoreArgs {
   int chained;             // 1: the kernel ahead in the stream is this library's own and writes none of
                            // q and k, so the K tiles may be fetched before that kernel has finished
 };
+// `split_ws` / `chunks`: optional query-range split (see col_scores_chunks); chunks = 1 or a null
+// workspace gives every key block one CTA that walks all query tiles.
 cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
-                              const AttnShape& s, cudaStream_t stream);
+                              const AttnShape& s, void* split_ws, int chunks, cudaStream_t stream);
+int col_scores_chunks(const AttnShape& s, int mode, int num_sms, size_t ws_bytes);
+size_t col_scores_split_bytes(const AttnShape& s, int mode, int chunks);
 // Keyformer row statistic: writes lse2' [B,H,Sq] of (s + g) / tau
 cudaError_t launch_kf_rowstat(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
                               float* lse2_out, const AttnShape& s, cudaStream_t stream);

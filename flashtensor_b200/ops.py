@@ -67,6 +67,17 @@ def _same_device(*ts):
       raise RuntimeError("all tensors must be on the same device")
 
 
+def _scratch(query, name, params, device):
+  """Optional scratch a kernel can use to split its work items when a launch has too few of them
+  to fill the device (None when it would not help).  The caching allocator keeps the block alive
+  until the stream's work that uses it has run."""
+  nbytes = ctypes.c_size_t(0)
+  _lib.check(name, query(ctypes.byref(params), ctypes.byref(nbytes)))
+  if nbytes.value == 0:
+    return None
+  return torch.empty((nbytes.value,), dtype=torch.uint8, device=device)
+
+
 def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None, softcap=0.0):
   """out = softmax(q k^T * scale (+ causal mask)) v.  q: [B,Sq,H,128]; k, v: [B,Skv,H,128].
   softcap > 0 applies cap * tanh(logits / cap) before the mask (cases/kernels/gemma2.py:30-33)."""
@@ -79,7 +90,10 @@ def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None
     lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32,
                       device=q4.device) if return_lse else None
     p = _lib.AttnParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(lse),
-                        float(softmax_scale), int(bool(causal)), float(softcap))
+                        float(softmax_scale), int(bool(causal)), float(softcap), None, 0)
+    ws = _scratch(lib.asuka_b200_attn_workspace_bytes, "asuka_b200_attn_workspace_bytes", p, q4.device)
+    if ws is not None:
+      p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     _lib.check("asuka_b200_attn_fwd", lib.asuka_b200_attn_fwd(ctypes.byref(p), _stream(q4)))
   out = out.view(q.shape) if q.dim() == 2 else out
   return (out, lse) if return_lse else out
@@ -100,7 +114,10 @@ def col_scores(q, k, lse, mode=_lib.SCORE_SUM, causal=True, softmax_scale=0.0, e
     score_sq = torch.empty_like(score) if mode == _lib.SCORE_SUM_SQ else None
     p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _desc(score), _desc(score_sq),
                          _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
-                         int(bool(causal)), int(mode), _desc(corm_mask))
+                         int(bool(causal)), int(mode), _desc(corm_mask), None, 0)
+    ws = _scratch(lib.asuka_b200_col_scores_workspace_bytes, "asuka_b200_col_scores_workspace_bytes", p, q4.device)
+    if ws is not None:
+      p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     _lib.check("asuka_b200_col_scores", lib.asuka_b200_col_scores(ctypes.byref(p), _stream(q4)))
   return (score, score_sq) if score_sq is not None else score
 
@@ -226,8 +243,8 @@ def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None,
                         _desc(roco_mean), _desc(roco_std))
     if workspace is None:
       nbytes = ctypes.c_size_t(0)
-      _lib.check("asuka_b200_case_workspace_bytes",
-                 lib.asuka_b200_case_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)))
+      _lib.check("asuka_b200_case_workspace_bytes_split",
+                 lib.asuka_b200_case_workspace_bytes_split(ctypes.byref(p), ctypes.byref(nbytes)))
       workspace = torch.empty((max(nbytes.value, 16),), dtype=torch.uint8, device=dev)
     _lib.check(fn_name, getattr(lib, fn_name)(ctypes.byref(p), ctypes.c_void_p(workspace.data_ptr()),
                                               ctypes.c_size_t(workspace.numel()), _stream(q4)))

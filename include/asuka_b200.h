@@ -78,9 +78,17 @@ typedef struct {
                           (torch.triu(-inf, diagonal=kv_len-q_len+1), cases/kernels/attn.py:22-23) */
   float softcap;       /* > 0: logits -> softcap * tanh(logits / softcap) before the mask, the
                           Gemma-2 variant (cases/kernels/gemma2.py:30-33); 0: off */
+  void* workspace;     /* optional device scratch (256-byte aligned; may be NULL).  With few (batch,
+                          head) units -- one GPU's share of a problem split over several -- the
+                          kernel divides every work item's key range over several CTAs and parks
+                          their partial results here; without it such launches leave SMs idle. */
+  uint64_t workspace_bytes;
 } asuka_attn_params;
 
 int asuka_b200_attn_fwd(const asuka_attn_params* p, asuka_stream stream);
+/* Scratch that lets asuka_b200_attn_fwd split key ranges on the current device for these shapes
+ * (0 when the launch fills the device anyway).  Any smaller workspace is accepted too. */
+int asuka_b200_attn_workspace_bytes(const asuka_attn_params* p, size_t* bytes);
 
 /* ---- per-key column reductions of the attention probabilities: replaces the generated
  *      column kernel for h2o_score (cases/kernels/h2o.py:35-36), roco_score / roco_sq_score
@@ -108,9 +116,16 @@ typedef struct {
   int32_t mode;          /* asuka_score_mode */
   asuka_tensor corm_mask; /* mode ASUKA_SCORE_CORM: [Sq, Skv] f32 thresholds (1/(i+1) in the reference's
                              prepare, cases/kernels/corm.py:46-48), shared by every batch and head */
+  void* workspace;        /* optional device scratch (256-byte aligned; may be NULL): with few (batch,
+                             head) units the query rows are divided over several CTAs per key block,
+                             whose partial sums are parked here and added in a fixed order */
+  uint64_t workspace_bytes;
 } asuka_score_params;
 
 int asuka_b200_col_scores(const asuka_score_params* p, asuka_stream stream);
+/* Scratch that lets asuka_b200_col_scores split the query rows on the current device (0 when the
+ * launch fills the device anyway).  Any smaller workspace is accepted too. */
+int asuka_b200_col_scores_workspace_bytes(const asuka_score_params* p, size_t* bytes);
 
 /* Row statistic of Keyformer's perturbed softmax (base-2 log-sum-exp of (s + g)/tau per query
  * row), the input `lse` of asuka_b200_col_scores in mode ASUKA_SCORE_PERTURBED.  Uses q, k,
@@ -196,7 +211,10 @@ int asuka_b200_linattn32_fwd(const asuka_linattn32_params* p, asuka_stream strea
  *      `workspace` holds the row statistics between the kernels: two arrays of B*H*Sq floats
  *      (unperturbed and Keyformer's perturbed one), each rounded up to 256 bytes, plus, when k
  *      and v have fewer heads than q, B*H*Skv floats for the per-query-head scores ahead of the
- *      group mean.  asuka_b200_case_workspace_bytes gives the exact figure. ---- */
+ *      group mean.  asuka_b200_case_workspace_bytes gives that figure, which is required.
+ *      asuka_b200_case_workspace_bytes_split adds, for launches with too few (batch, head) units
+ *      to fill the current device, the scratch that lets the kernels split their work items
+ *      further; a workspace between the two sizes is accepted and used as far as it goes. ---- */
 typedef struct {
   asuka_tensor q, k, v, out;
   asuka_tensor score;    /* h2o_score | kf_score | roco_score, [B, H, Skv] f32 */
@@ -214,6 +232,7 @@ typedef struct {
 } asuka_case_params;
 
 int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes);
+int asuka_b200_case_workspace_bytes_split(const asuka_case_params* p, size_t* bytes);
 /* H2O.forward, cases/kernels/h2o.py:18-38 (+ selection) */
 int asuka_b200_h2o(const asuka_case_params* p, void* workspace, size_t workspace_bytes,
                    asuka_stream stream);

@@ -542,7 +542,7 @@ def test_no_store_lands_outside_outputs_or_workspace(ops, shape):
   def ws_for(**kw):
     p = _lib.CaseParams(ops._desc(q), ops._desc(k), ops._desc(v))
     n = ctypes.c_size_t(0)
-    assert lib.asuka_b200_case_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
+    assert lib.asuka_b200_case_workspace_bytes_split(ctypes.byref(p), ctypes.byref(n)) == 0
     return mem.take((n.value,), torch.uint8)
 
   # H2O with the recent window, RoCo with statistics, Keyformer with both noise sources
@@ -625,9 +625,10 @@ def test_full_size_h2o_properties(ops):
   torch.cuda.synchronize()
   # (a) a head's scores sum to the number of query rows
   torch.testing.assert_close(score.sum(-1), torch.full((B, H), float(S), device="cuda"), rtol=1e-4, atol=0.05)
-  # (b) causality: the first 1024 rows equal the computation on the first 1024 tokens alone
+  # (b) causality: the first 1024 rows equal the computation on the first 1024 tokens alone (up to
+  # rounding: the shorter problem may divide its key ranges differently over the CTAs)
   out_p, score_p = ops.h2o(q[:, :1024], k[:, :1024], v[:, :1024])
-  assert torch.equal(out[:, :1024], out_p)
+  torch.testing.assert_close(out[:, :1024].float(), out_p.float(), rtol=0, atol=4e-3)
   # (c) a constant V gives a constant output
   vc = torch.full_like(v, 0.5)
   oc = ops.attn_fwd(q, k, vc)
