@@ -680,63 +680,74 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
-// Combines the parts of a key-range split.  One warp per query row, lane = four output columns:
-// every part's reference, row sum and 512-byte O row are read (they were written moments ago and
-// sit in L2) with all loads of a row in flight at once, scaled to the common reference and added
-// in part order, so the result does not depend on which part finished first.
-constexpr int kMaxParts = 8;
-constexpr int kMergeRows = 8;  // rows (= warps) per CTA
+// Combines the parts of a key-range split.  A warp takes four query rows, lane = four output
+// columns: every part's reference, row sum and 512-byte O row are read (they were written moments
+// ago and sit in L2) with all loads of the four rows in flight at once -- the kernel is bound by
+// that latency, not by the bytes -- scaled to the common reference and added in part order, so the
+// result does not depend on which part finished first.
+constexpr int kMaxParts = 4;
+constexpr int kMergeWarps = 8;
+constexpr int kMergeRowsPerWarp = 4;
+constexpr int kMergeRows = kMergeWarps * kMergeRowsPerWarp;  // rows per CTA (divides the tile height)
 template <bool kBF16>
-__global__ void __launch_bounds__(kMergeRows * 32) attn_merge_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(kMergeWarps * 32) attn_merge_kernel(const FwdParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = p.B * p.H;
   const int rb = static_cast<int>(blockIdx.x) / bh_count;  // block of kMergeRows query rows
   const int bh = static_cast<int>(blockIdx.x) % bh_count;
   const int b = bh / p.H, h = bh % p.H;
-  const int row = rb * kMergeRows + warp;
-  const int q0 = (row / kTile) * kTile;
-  // the same arithmetic as get_item: the parts of the 256-row block this row's tile belongs to
-  const int qa = (row / (2 * kTile)) * 2 * kTile;
+  const int row0 = rb * kMergeRows + warp * kMergeRowsPerWarp;
+  const int q0 = (row0 / kTile) * kTile;
+  // the same arithmetic as decode_item: the parts of the 256-row block these rows' tile belongs to
+  const int qa = (row0 / (2 * kTile)) * 2 * kTile;
   const int len = (max(kv_tiles_for(qa, p), kv_tiles_for(qa + kTile, p)) + p.parts - 1) / p.parts;
   const int nparts = (kv_tiles_for(q0, p) + len - 1) / len;
   griddep_wait();               // the parts are the output of the kernel ahead
   griddep_launch_dependents();
-  if (nparts <= 1 || row >= p.Sq) return;  // (one part: the forward kernel wrote the result itself)
-  const size_t prow = (static_cast<size_t>(bh) * p.Sq + row) * p.parts;
-  float2 ml[kMaxParts];
-  float4 o[kMaxParts];
+  if (nparts <= 1) return;      // (one part: the forward kernel wrote the result itself)
+  float2 ml[kMergeRowsPerWarp][kMaxParts];
+  float4 o[kMergeRowsPerWarp][kMaxParts];
 #pragma unroll
-  for (int q = 0; q < kMaxParts; ++q) {
-    if (q < nparts) {
-      ml[q] = *reinterpret_cast<const float2*>(p.part_ml + (prow + q) * 2);
-      o[q] = *reinterpret_cast<const float4*>(p.part_o + (prow + q) * 128 + lane * 4);
+  for (int r = 0; r < kMergeRowsPerWarp; ++r) {
+    const size_t prow = (static_cast<size_t>(bh) * p.Sq + min(row0 + r, p.Sq - 1)) * p.parts;
+#pragma unroll
+    for (int q = 0; q < kMaxParts; ++q) {
+      if (q < nparts) {
+        ml[r][q] = *reinterpret_cast<const float2*>(p.part_ml + (prow + q) * 2);
+        o[r][q] = *reinterpret_cast<const float4*>(p.part_o + (prow + q) * 128 + lane * 4);
+      }
     }
   }
-  float m = -INFINITY;
 #pragma unroll
-  for (int q = 0; q < kMaxParts; ++q)
-    if (q < nparts) m = fmaxf(m, ml[q].x);
-  float l = 0.f;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < kMergeRowsPerWarp; ++r) {
+    const int row = row0 + r;
+    if (row >= p.Sq) break;
+    float m = -INFINITY;
 #pragma unroll
-  for (int q = 0; q < kMaxParts; ++q) {
-    if (q < nparts) {
-      const float w = ml[q].x > -INFINITY ? ex2(ml[q].x - m) : 0.f;
-      l = fmaf(w, ml[q].y, l);
-      acc.x = fmaf(w, o[q].x, acc.x);
-      acc.y = fmaf(w, o[q].y, acc.y);
-      acc.z = fmaf(w, o[q].z, acc.z);
-      acc.w = fmaf(w, o[q].w, acc.w);
+    for (int q = 0; q < kMaxParts; ++q)
+      if (q < nparts) m = fmaxf(m, ml[r][q].x);
+    float l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < kMaxParts; ++q) {
+      if (q < nparts) {
+        const float w = ml[r][q].x > -INFINITY ? ex2(ml[r][q].x - m) : 0.f;
+        l = fmaf(w, ml[r][q].y, l);
+        acc.x = fmaf(w, o[r][q].x, acc.x);
+        acc.y = fmaf(w, o[r][q].y, acc.y);
+        acc.z = fmaf(w, o[r][q].z, acc.z);
+        acc.w = fmaf(w, o[r][q].w, acc.w);
+      }
     }
+    const float inv_l = 1.f / l;
+    uint16_t* orow = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(b) * p.o_sb +
+                     static_cast<int64_t>(row) * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
+    uint2 v;
+    v.x = pack2<kBF16>(acc.x * inv_l, acc.y * inv_l);
+    v.y = pack2<kBF16>(acc.z * inv_l, acc.w * inv_l);
+    *reinterpret_cast<uint2*>(orow + lane * 4) = v;
+    if (p.lse2 != nullptr && lane == 0) p.lse2[static_cast<size_t>(bh) * p.Sq + row] = m + log2f(l);
   }
-  const float inv_l = 1.f / l;
-  uint16_t* orow = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(b) * p.o_sb +
-                   static_cast<int64_t>(row) * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
-  uint2 v;
-  v.x = pack2<kBF16>(acc.x * inv_l, acc.y * inv_l);
-  v.y = pack2<kBF16>(acc.z * inv_l, acc.w * inv_l);
-  *reinterpret_cast<uint2*>(orow + lane * 4) = v;
-  if (p.lse2 != nullptr && lane == 0) p.lse2[static_cast<size_t>(bh) * p.Sq + row] = m + log2f(l);
 }
 
 }  // namespace
@@ -779,7 +790,7 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.causal = s.causal;
   p.diag_off = s.Skv - s.Sq;
   p.nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
-  p.parts = parts > 1 && split_ws != nullptr ? parts : 1;
+  p.parts = parts > 1 && split_ws != nullptr ? (parts < kMaxParts ? parts : kMaxParts) : 1;
   p.n_items = p.nq_blocks * s.B * s.H * p.parts;
   p.group = s.group;
   p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
@@ -810,7 +821,7 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   count_launch();
   if (e != cudaSuccess || p.parts == 1) return e;
   const dim3 mgrid(static_cast<unsigned>((s.Sq + kMergeRows - 1) / kMergeRows) * s.B * s.H);
-  e = launch_dependent(s.bf16 ? attn_merge_kernel<true> : attn_merge_kernel<false>, mgrid, dim3(kMergeRows * 32), 0,
+  e = launch_dependent(s.bf16 ? attn_merge_kernel<true> : attn_merge_kernel<false>, mgrid, dim3(kMergeWarps * 32), 0,
                        stream, p);
   count_launch();
   return e;
