@@ -141,9 +141,9 @@ int check_dense(const asuka_tensor& t, int dtype, int ndim, const int64_t* shape
   return ASUKA_OK;
 }
 
-int make_map(CUtensorMap* m, const asuka_tensor& t) {
+int make_map(CUtensorMap* m, const asuka_tensor& t, uint32_t box_rows = 128) {
   int r = tma_host::make_bshd_map(m, t.ptr, t.dtype == ASUKA_BF16, t.shape[0], t.shape[1], t.shape[2],
-                                  t.shape[3], t.stride[0], t.stride[1], t.stride[2], 128);
+                                  t.shape[3], t.stride[0], t.stride[1], t.stride[2], box_rows);
   return r == 0 ? ASUKA_OK : ASUKA_ERR_CUDA;
 }
 
@@ -417,9 +417,13 @@ int sima_impl(const asuka_sima_params* p, void* ws, size_t ws_bytes, cudaStream_
   } else {
     mo = mq;
   }
+  const int sms = sm_count();
+  if (sms <= 0) return ASUKA_ERR_CUDA;
+  CUtensorMap m64[3];  // the same tensors in boxes of 64 rows, for the single-kernel path's first phase
+  if ((r = make_map(&m64[0], p->q, 64)) || (r = make_map(&m64[1], p->k, 64)) || (r = make_map(&m64[2], p->v, 64))) return r;
   return map_cuda(launch_sima(mq, mk, mv, mo, p->out.ptr, p->out.stride[0], p->out.stride[1],
                               p->out.stride[2], ws, sh, p->k.ptr, p->k.stride[0], p->k.stride[1],
-                              p->k.stride[2], stream));
+                              p->k.stride[2], m64, sms, stream));
 }
 
 // forward + column scores (+ selection) on one stream; the row statistic lives in `ws`

@@ -722,11 +722,489 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// All three steps in one persistent kernel (SimA; the launch picks it when there are enough
+// (batch, head) units to keep every group busy).  Four CTAs form a group that walks units; each
+// CTA owns a quarter of the sequence of the unit at hand:
+//   phase 1  statistics over its slab as in sima_stats_kernel, partial results into the group's
+//            slots of the workspace (a few MB for the whole grid: they never leave L2);
+//   barrier  a counter per unit, bounded wait;
+//   reduce   every CTA sums the four partials in slab order, normalises and writes M'' straight
+//            into its own shared memory in the layout the tensor pipe reads (same arithmetic, same
+//            order and same per-block scales as sima_reduce_kernel, so the same bits);
+//   phase 2  out = (Q M'') * inverse scale over the SAME slab, latest tile first.
+// The point is the second read of Q: it comes a few tens of microseconds after the first, from
+// the same 0.5 MB slab, while about 37 units are in flight; K and V are loaded with an
+// evict-first L2 policy, so Q (2 MB per unit) is still in L2 and the kernel's DRAM traffic is the
+// algorithmic minimum: q, k, v once in, out once out.  The grid is at most one CTA per SM, so
+// every CTA of a group is resident and the group barrier cannot starve.
+// ---------------------------------------------------------------------------------------------
+constexpr int kFuThreads = 384;  // warp 0 producer, warp 1 MMA, warps 4-11 statistics and reduce, warps 4-7 epilogue
+constexpr int kFuGroup = 4;      // CTAs per unit = blocks of 32 output channels in the reduce
+constexpr uint32_t kFuSmem = 7 * kTileBytes + 1024;  // phase 1: 2 x [K|V|Q]; phase 2: M'', 4 Q stages, 2 staging
+static_assert(kFuGroup == 4, "the reduce below assigns one block of 32 output channels per partial slot");
+
+struct FusedParams {
+  int B, H, S;
+  int n_units, n_groups;
+  int ntiles, tiles_per_cta;
+  float* part_m;      // [n_groups][4][e][d]
+  float* part_c;      // [n_groups][4][2][128]
+  uint32_t* arrive;   // [n_units], zero at launch: CTAs of the unit whose partials are written
+  uint32_t* rdone;    // [n_units], zero at launch: CTAs of the unit that have read all partials
+  float* out_f32;
+  int64_t o_sb, o_ss, o_sh;
+  uint32_t* status;
+  uint32_t stagger_ns;  // head start of the even groups over the odd ones
+};
+
+struct FuBars {
+  uint64_t full[4], empty[4], m_done;  // (four phase-1 stages)
+  uint64_t q_full[4], q_empty[4], acc_full[2], acc_empty[2];
+};
+
+// waits (bounded) until *ctr >= want; false on time-out
+__device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t want, volatile uint32_t* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(ctr) < want) {
+    if (((++spins) & 31u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > SM100_WAIT_NS) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+  return true;
+}
+
+template <bool kBF16, bool kOutF32>
+__global__ void __launch_bounds__(kFuThreads, 1)
+sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q64,
+                  const __grid_constant__ CUtensorMap map_k64, const __grid_constant__ CUtensorMap map_v64,
+                  const __grid_constant__ CUtensorMap map_o, const FusedParams p) {
+  // Phase 1 streams 64 rows of [K | V | Q] per stage through four stages: the consumers are fast, so
+  // about three stages (144 KB) are in flight per SM, which is what the HBM latency asks for;
+  // two stages of 128 rows leave one in flight and the kernel latency-bound at 0.8 of the bandwidth.
+  constexpr int kSt = 4, kQ = 4;
+  constexpr int kRows1 = 64;
+  constexpr uint32_t kSubBytes = kRows1 * 128 * 2;  // one operand's 64 rows: two 64-column halves
+  constexpr uint32_t kSubHalf = kSubBytes / 2;
+  constexpr uint32_t kStageBytes = 3 * kSubBytes;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) FuBars bars;
+  __shared__ float inv_c[kTile];
+  __shared__ float wmax[4][8];
+  __shared__ float inv4_s[4];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_s;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sM = smem_base;                  // phase 2 layout
+  const uint32_t sQ = smem_base + kTileBytes;
+  const uint32_t sO = sQ + kQ * kTileBytes;
+  // phase 1's cross-warp sums sit behind its two stages, in memory phase 2 uses for staging
+  float (*red)[8][kTile] = reinterpret_cast<float (*)[8][kTile]>(smem_gen + kSt * kStageBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile uint32_t* abortp = &abort_s;
+  const int group = static_cast<int>(blockIdx.x) / kFuGroup;
+  const int c = static_cast<int>(blockIdx.x) % kFuGroup;
+  const int tile0 = c * p.tiles_per_cta;
+  const int ntile = max(0, min(p.tiles_per_cta, p.ntiles - tile0));
+  float* my_pm = p.part_m + (static_cast<size_t>(group) * kFuGroup + c) * kMElems;
+  float* my_pc = p.part_c + (static_cast<size_t>(group) * kFuGroup + c) * 2 * kTile;
+  const float* grp_pm = p.part_m + static_cast<size_t>(group) * kFuGroup * kMElems;
+  const float* grp_pc = p.part_c + static_cast<size_t>(group) * kFuGroup * 2 * kTile;
+
+  if (tid == 0) {
+    abort_s = 0;
+    for (int i = 0; i < kSt; ++i) {
+      mbar_init(smem_u32(&bars.full[i]), 1);
+      mbar_init(smem_u32(&bars.empty[i]), 1 + 8);
+    }
+    mbar_init(smem_u32(&bars.m_done), 1);
+    for (int i = 0; i < kQ; ++i) {
+      mbar_init(smem_u32(&bars.q_full[i]), 1);
+      mbar_init(smem_u32(&bars.q_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.acc_full[i]), 1);
+      mbar_init(smem_u32(&bars.acc_empty[i]), 128);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_q64);
+    tma_prefetch_desc(&map_k64);
+    tma_prefetch_desc(&map_v64);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_s), 512);  // M accumulator | two output accumulators
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tM = tmem_base_s, tAcc = tmem_base_s + 128;
+  // Every group does the same work per unit, so all of them would switch between the read-heavy
+  // first phase and the write-heavy second one at the same moments, and the memory system would
+  // idle through every switch and every group barrier.  Odd groups therefore start a little under
+  // half a unit late, once; after that the two halves of the grid stay out of step and fill each
+  // other's gaps (measured at B8 H32 S8192: 455 -> 421 us).
+  if (group & 1) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < p.stagger_ns) __nanosleep(500);
+  }
+  const uint64_t evict_first = l2_policy_evict_first();
+  const uint64_t evict_last = l2_policy_evict_last();
+
+  // Counts that run on over the units, from which ring stages and barrier parities follow; every
+  // role advances them the same way (ntile is the same for every unit of this CTA).
+  uint32_t n1 = 0, n2 = 0, nu = 0;  // phase-1 steps, phase-2 tiles, units done so far
+  int prev_u = -1;
+  bool ok = true;
+  const int nstep = ntile * (kTile / kRows1);  // phase-1 steps of 64 rows
+
+  for (int u = group; u < p.n_units; u += p.n_groups, n1 += nstep, n2 += ntile, ++nu) {
+    const int b = u / p.H, h = u % p.H;
+    // ------------------------------------------------------------------------------ phase 1
+    if (warp == 0) {
+      if (lane == 0) {
+        for (int i = 0; i < nstep; ++i) {
+          const uint32_t k = n1 + i;
+          const int st = k % kSt;
+          if (k >= kSt && !mbar_wait(smem_u32(&bars.empty[st]), (k / kSt - 1) & 1, abortp)) {
+            record_timeout(p.status, 61);
+            break;
+          }
+          const uint32_t bar = smem_u32(&bars.full[st]);
+          const uint32_t base = smem_base + st * kStageBytes;
+          const int s0 = tile0 * kTile + i * kRows1;
+          mbar_expect_tx(bar, kStageBytes);
+          tma_load_4d_hint(base, &map_k64, bar, 0, h, s0, b, evict_first);
+          tma_load_4d_hint(base + kSubHalf, &map_k64, bar, 64, h, s0, b, evict_first);
+          tma_load_4d_hint(base + kSubBytes, &map_v64, bar, 0, h, s0, b, evict_first);
+          tma_load_4d_hint(base + kSubBytes + kSubHalf, &map_v64, bar, 64, h, s0, b, evict_first);
+          tma_load_4d_hint(base + 2 * kSubBytes, &map_q64, bar, 0, h, s0, b, evict_last);
+          tma_load_4d_hint(base + 2 * kSubBytes + kSubHalf, &map_q64, bar, 64, h, s0, b, evict_last);
+        }
+      }
+    } else if (warp == 1) {
+      constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+      constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_MN_MAJOR, UMMA_MN_MAJOR, 128, 128);
+      bool good = true;
+      for (int i = 0; i < nstep && good; ++i) {
+        const uint32_t k = n1 + i;
+        const int st = k % kSt;
+        good = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (k / kSt) & 1, abortp));
+        if (!good) { if (lane == 0) record_timeout(p.status, 62); break; }
+        tc_fence_after_sync();
+        const uint32_t base = smem_base + st * kStageBytes;
+        const uint64_t adesc = umma_smem_desc_sw128(base, kSubHalf, 1024);              // K
+        const uint64_t bdesc = umma_smem_desc_sw128(base + kSubBytes, kSubHalf, 1024);  // V
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < kRows1 / 16; ++kk) {
+            const uint64_t off = static_cast<uint64_t>(kk * (2048 >> 4));
+            umma_ss(tM, adesc + off, bdesc + off, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars.empty[st]));
+        }
+        __syncwarp();
+      }
+      if (good && ntile > 0 && elect_one()) umma_commit(smem_u32(&bars.m_done));
+      __syncwarp();
+    } else if (warp >= 4) {
+      const int which = (warp - 4) >> 2;  // 0 = K, 1 = Q
+      const int t128 = tid - 128 - which * 128;
+      const int chunk16 = t128 & 15;
+      const int rg = t128 >> 4;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      bool good = true;
+      for (int i = 0; i < nstep; ++i) {
+        const uint32_t k = n1 + i;
+        const int st = k % kSt;
+        good = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (k / kSt) & 1, abortp));
+        if (!good) { if (lane == 0) record_timeout(p.status, 63); break; }
+        const uint8_t* tile = smem_gen + st * kStageBytes + (which ? 2 * kSubBytes : 0) +
+                              (chunk16 >> 3) * kSubHalf;
+#pragma unroll
+        for (int r = 0; r < kRows1 / 8; ++r) {
+          const int row = rg + 8 * r;
+          const uint4 v = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
+          abs_acc8<kBF16>(v, acc);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) red[which][rg][chunk16 * 8 + i] = acc[i];
+      named_bar_sync(1 + which, 128);
+      // the group's slots still hold the previous unit's partials until every CTA of the group has
+      // read them (by now it has, long ago; the wait costs one load)
+      if (prev_u >= 0 && good) good = wait_counter(p.rdone + prev_u, kFuGroup, abortp);
+      float sum = 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) sum += red[which][g][t128];
+      my_pc[which * kTile + t128] = sum;
+      if (which == 0) {
+        const int wq = warp & 3;
+        const int d = wq * 32 + lane;
+        if (ntile > 0) {
+          good = good && __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.m_done), nu & 1, abortp));
+          if (good) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              uint32_t uu[32];
+              tmem_ld32(tM + (static_cast<uint32_t>(wq * 32) << 16) + cc * 32, uu);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) my_pm[(cc * 32 + i) * kTile + d] = __uint_as_float(uu[i]);
+            }
+          } else if (lane == 0) {
+            record_timeout(p.status, 64);
+          }
+        } else {
+          for (int i = 0; i < 128; ++i) my_pm[i * kTile + d] = 0.f;
+        }
+      }
+      if (!good) *abortp = 1u;
+    }
+    // ------------------------------------------------------------------------------ group barrier
+    __threadfence();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (tid == 0) {
+      atomicAdd(p.arrive + u, 1u);
+      if (!wait_counter(p.arrive + u, kFuGroup, abortp)) record_timeout(p.status, 65);
+    }
+    __syncthreads();
+    if (*abortp) { ok = false; break; }
+    // ------------------------------------------------------------------------------ reduce
+    if (warp >= 4) {
+      const int t256 = tid - 128;
+      if (t256 < kTile) {
+        float ck = 0.f, cq = 0.f;
+        for (int cc = 0; cc < kFuGroup; ++cc) {
+          ck += __ldcg(grp_pc + (cc * 2 + 0) * kTile + t256);
+          cq += __ldcg(grp_pc + (cc * 2 + 1) * kTile + t256);
+        }
+        inv_c[t256] = __fdiv_rn(1.0f, __fmul_rn(ck, cq));
+      }
+      named_bar_sync(3, 256);
+      float vals[4][16];
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) {
+        float amax = 0.f;
+#pragma unroll
+        for (int it = 0; it < 16; ++it) {
+          const int idx = it * 256 + t256;  // = e_local * 128 + d
+          float m = 0.f;
+#pragma unroll
+          for (int cc = 0; cc < kFuGroup; ++cc) m += __ldcg(grp_pm + static_cast<size_t>(cc) * kMElems + blk * kRedElems + idx);
+          m *= inv_c[idx & 127];
+          vals[blk][it] = m;
+          amax = fmaxf(amax, fabsf(m));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) wmax[blk][warp - 4] = amax;
+      }
+      __threadfence();
+      named_bar_sync(3, 256);
+      if (t256 == 0) atomicAdd(p.rdone + u, 1u);  // every partial of this unit has been read by this CTA
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) {
+        float a = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a = fmaxf(a, wmax[blk][i]);
+        float sc = 1.f;
+        if (a > 0.f && a < INFINITY) {
+          int ex;
+          frexpf(a, &ex);
+          sc = ldexpf(1.0f, 14 - ex);
+        }
+        if (t256 == 0) inv4_s[blk] = 1.0f / sc;
+#pragma unroll
+        for (int it = 0; it < 16; ++it) {
+          const int idx = it * 256 + t256;
+          const int e = blk * 32 + (idx >> 7), d = idx & 127;
+          const float v = vals[blk][it] * sc;
+          uint16_t bits;
+          if constexpr (kBF16) {
+            __nv_bfloat16 hb = __float2bfloat16_rn(v);
+            bits = *reinterpret_cast<uint16_t*>(&hb);
+          } else {
+            __half hh = __float2half_rn(v);
+            bits = *reinterpret_cast<uint16_t*>(&hh);
+          }
+          // M''^T [e][d], d contiguous: the K-major B operand, two 64-element halves, 128-byte swizzle
+          *reinterpret_cast<uint16_t*>(smem_gen + (d >> 6) * kHalfBytes + sw128_offset(e, (d & 63) >> 3) + (d & 7) * 2) = bits;
+        }
+      }
+      fence_proxy_async_smem();  // written by ordinary stores, read by the tensor pipe
+    }
+    __syncthreads();
+    // ------------------------------------------------------------------------------ phase 2
+    if (warp == 0) {
+      if (lane == 0) {
+        for (int i = 0; i < ntile; ++i) {
+          const uint32_t k = n2 + i;
+          const int st = k % kQ;
+          if (k >= kQ && !mbar_wait(smem_u32(&bars.q_empty[st]), (k / kQ - 1) & 1, abortp)) {
+            record_timeout(p.status, 66);
+            break;
+          }
+          const uint32_t bar = smem_u32(&bars.q_full[st]);
+          const int s0 = (tile0 + ntile - 1 - i) * kTile;  // latest tile first: the freshest in L2
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d_hint(sQ + st * kTileBytes, &map_q, bar, 0, h, s0, b, evict_first);
+          tma_load_4d_hint(sQ + st * kTileBytes + kHalfBytes, &map_q, bar, 64, h, s0, b, evict_first);
+        }
+      }
+    } else if (warp == 1) {
+      constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+      constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
+      const uint64_t mdesc = umma_smem_desc_sw128(sM, 16, 1024);
+      bool good = true;
+      for (int i = 0; i < ntile && good; ++i) {
+        const uint32_t k = n2 + i;
+        const int st = k % kQ, buf = k & 1;
+        good = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_full[st]), (k / kQ) & 1, abortp));
+        if (good && k >= 2)
+          good = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_empty[buf]), ((k >> 1) - 1) & 1, abortp));
+        if (!good) { if (lane == 0) record_timeout(p.status, 67); break; }
+        tc_fence_after_sync();
+        const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+            umma_ss(tAcc + buf * 128, qdesc + off, mdesc + off, idesc, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars.acc_full[buf]));
+          umma_commit(smem_u32(&bars.q_empty[st]));
+        }
+        __syncwarp();
+      }
+    } else if (warp >= 4 && warp < 8) {
+      const int wq = warp & 3;
+      const int r = wq * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+      const float inv4[4] = {inv4_s[0], inv4_s[1], inv4_s[2], inv4_s[3]};
+      bool good = true;
+      for (int i = 0; i < ntile && good; ++i) {
+        const uint32_t k = n2 + i;
+        const int buf = k & 1;
+        const int s0 = (tile0 + ntile - 1 - i) * kTile;
+        good = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_full[buf]), (k >> 1) & 1, abortp));
+        if (!good) { if (lane == 0) record_timeout(p.status, 68); break; }
+        tc_fence_after_sync();
+        if constexpr (!kOutF32) {
+          if (tid == 128) tma_store_wait_read_n<1>();
+        }
+        named_bar_sync(1, 128);
+        uint8_t* stage = smem_gen + (sO - smem_base) + (kOutF32 ? 0 : buf * kTileBytes);
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t uu[32];
+          tmem_ld32(tAcc + lane_base + buf * 128 + cc * 32, uu);
+          tmem_wait_ld();
+          const float inv_sc = inv4[cc];
+          if constexpr (kOutF32) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              float4 v;
+              v.x = __uint_as_float(uu[g * 4 + 0]) * inv_sc;
+              v.y = __uint_as_float(uu[g * 4 + 1]) * inv_sc;
+              v.z = __uint_as_float(uu[g * 4 + 2]) * inv_sc;
+              v.w = __uint_as_float(uu[g * 4 + 3]) * inv_sc;
+              const int chunk = cc * 8 + g;
+              *reinterpret_cast<float4*>(stage + r * 512 + ((chunk ^ (r & 31)) << 4)) = v;
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float lo = __uint_as_float(uu[g * 8 + 2 * q]) * inv_sc;
+                const float hi = __uint_as_float(uu[g * 8 + 2 * q + 1]) * inv_sc;
+                if constexpr (kBF16) {
+                  __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi);
+                  w[q] = *reinterpret_cast<uint32_t*>(&t2);
+                } else {
+                  __half2 t2 = __floats2half2_rn(lo, hi);
+                  w[q] = *reinterpret_cast<uint32_t*>(&t2);
+                }
+              }
+              const int chunk = cc * 4 + g;
+              *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes + sw128_offset(r, chunk & 7)) =
+                  make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+        if constexpr (kOutF32) {
+          named_bar_sync(1, 128);
+          for (int rr = wq; rr < kTile; rr += 4) {
+            const int srow = s0 + rr;
+            if (srow < p.S) {
+              const float4 v = *reinterpret_cast<const float4*>(stage + rr * 512 + (lane << 4));
+              const int chunk = lane ^ (rr & 31);
+              float* o = p.out_f32 + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(srow) * p.o_ss +
+                         static_cast<int64_t>(h) * p.o_sh + chunk * 4;
+              *reinterpret_cast<float4*>(o) = v;
+            }
+          }
+        } else {
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (tid == 128) {
+#ifdef ASUKA_SIMA_STORE_PLAIN
+            tma_store_4d(&map_o, sO + buf * kTileBytes, 0, h, s0, b);
+            tma_store_4d(&map_o, sO + buf * kTileBytes + kHalfBytes, 64, h, s0, b);
+#else
+            tma_store_4d_hint(&map_o, sO + buf * kTileBytes, 0, h, s0, b, evict_first);
+            tma_store_4d_hint(&map_o, sO + buf * kTileBytes + kHalfBytes, 64, h, s0, b, evict_first);
+#endif
+            tma_store_commit();
+          }
+        }
+      }
+      if constexpr (!kOutF32) {
+        if (tid == 128) tma_store_wait_read();  // phase 1 of the next unit reuses the staging memory
+      }
+      if (!good) *abortp = 1u;
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (*abortp) { ok = false; break; }
+    prev_u = u;
+  }
+  (void)ok;
+  (void)evict_last;
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base_s, 512);
+  }
+}
+
 size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 struct Plan {
   int ntiles, nchunks, tiles_per_chunk;
-  size_t off_pm, off_pc, off_m16, off_sc, off_cmax, total;
+  size_t off_pm, off_pc, off_m16, off_sc, off_cmax, off_cnt, total;
 };
 
 Plan make_plan(const SimaShape& s) {
@@ -745,6 +1223,7 @@ Plan make_plan(const SimaShape& s) {
   pl.off_m16 = off; off = align256(off + static_cast<size_t>(bh) * kMElems * 2);
   pl.off_sc = off; off = align256(off + static_cast<size_t>(bh) * kRedBlocks * 4);
   pl.off_cmax = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * kTile * 4);
+  pl.off_cnt = off; off = align256(off + static_cast<size_t>(bh) * 2 * sizeof(uint32_t));  // fused kernel's counters
   pl.total = off;
   return pl;
 }
@@ -757,10 +1236,51 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
                         const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
                         int64_t out_stride_s, int64_t out_stride_h, void* ws, const SimaShape& s,
                         const void* k_ptr, int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
-                        cudaStream_t stream) {
+                        const CUtensorMap* maps64, int num_sms, cudaStream_t stream) {
   const Plan pl = make_plan(s);
   const int bh = s.B * s.H;
   uint8_t* w = static_cast<uint8_t*>(ws);
+  // One persistent kernel for all three steps when there are enough units to keep every group of
+  // four CTAs busy for a few rounds (and the partial slots fit the workspace plan above).
+  const int n_groups = num_sms / kFuGroup;
+#ifdef ASUKA_SIMA_NO_FUSED
+  const bool fused = false;
+#else
+  const bool fused = !s.ea && maps64 != nullptr && n_groups > 0 && bh >= 2 * n_groups && pl.ntiles >= kFuGroup &&
+                     static_cast<long long>(bh) * pl.nchunks >= static_cast<long long>(n_groups) * kFuGroup;
+#endif
+  if (fused) {
+    FusedParams fp;
+    fp.B = s.B; fp.H = s.H; fp.S = s.S;
+    fp.n_units = bh;
+    fp.n_groups = n_groups;
+    fp.ntiles = pl.ntiles;
+    fp.tiles_per_cta = (pl.ntiles + kFuGroup - 1) / kFuGroup;
+    fp.part_m = reinterpret_cast<float*>(w + pl.off_pm);
+    fp.part_c = reinterpret_cast<float*>(w + pl.off_pc);
+    fp.arrive = reinterpret_cast<uint32_t*>(w + pl.off_cnt);
+    fp.rdone = fp.arrive + bh;
+    fp.out_f32 = s.out_f32 ? static_cast<float*>(out_ptr) : nullptr;
+    fp.o_sb = out_stride_b; fp.o_ss = out_stride_s; fp.o_sh = out_stride_h;
+    fp.status = device_status_words();
+    {
+      // a unit costs a CTA five passes over its slab (K, V, Q in; Q again from L2; out) at its
+      // share of the memory bandwidth, about 44 bytes per nanosecond per SM on this part
+      const double unit_ns = static_cast<double>(fp.tiles_per_cta) * kTile * 128 * 2 * 5 / 44.0;
+      fp.stagger_ns = static_cast<uint32_t>(0.4 * unit_ns);
+    }
+    cudaError_t e = cudaMemsetAsync(fp.arrive, 0, static_cast<size_t>(bh) * 2 * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+    void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, FusedParams);
+    if (s.out_f32) kern = s.bf16 ? sima_fused_kernel<true, true> : sima_fused_kernel<false, true>;
+    else kern = s.bf16 ? sima_fused_kernel<true, false> : sima_fused_kernel<false, false>;
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(kFuSmem));
+    if (e != cudaSuccess) return e;
+    kern<<<static_cast<unsigned>(n_groups * kFuGroup), kFuThreads, kFuSmem, stream>>>(mq, maps64[0], maps64[1], maps64[2],
+                                                                                      s.out_f32 ? mq : mo, fp);
+    count_launch();
+    return cudaGetLastError();
+  }
   StatsParams sp;
   sp.B = s.B; sp.H = s.H; sp.S = s.S;
   sp.nchunks = pl.nchunks; sp.tiles_per_chunk = pl.tiles_per_chunk; sp.ntiles = pl.ntiles;

@@ -204,6 +204,24 @@ def test_sima_vs_oracle(ops, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(10, 700, 8), (3, 1000, 32), (80, 512, 1), (2, 1664, 40)])
+def test_sima_with_many_units_vs_oracle(ops, shape, dtype):
+  # enough (batch, head) units that the single persistent kernel runs (groups of four CTAs walk the
+  # units, each CTA a quarter of the sequence); ragged lengths, a quarter with no tile at all
+  B, S, H = shape
+  q, k, v = O.make_inputs("sima", B, S, S, H, 128, dtype, seed=S)
+  ref = O.sima(q, k, v)
+  qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+  out16 = ops.sima_fwd(qd, kd, vd)
+  out32 = ops.sima_fwd(qd, kd, vd, out_dtype=torch.float32)
+  torch.cuda.synchronize()
+  close(out32, ref, "sima f32 out")
+  close(out16, ref, "sima 16-bit out")
+  assert torch.equal(out32, ops.sima_fwd(qd, kd, vd, out_dtype=torch.float32))   # run-to-run identical
+  no_timeouts(ops)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 128, 1), (2, 1000, 3), (1, 4096, 4), (3, 2500, 2)])
 def test_ea_vs_oracle(ops, shape, dtype):
   # bench/ea.mlir:13-17: softmax over the features of q, softmax over the sequence of k
