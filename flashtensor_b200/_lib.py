@@ -78,6 +78,7 @@ SYMBOLS = {
     "asuka_b200_strerror": (ctypes.c_char_p, [ctypes.c_int]),
     "asuka_b200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "asuka_b200_launch_count": (ctypes.c_uint64, []),
+    "asuka_b200_selftest_wait_timeout": (ctypes.c_int, [ctypes.c_uint32, ctypes.c_void_p]),
     "asuka_b200_attn_fwd": (ctypes.c_int, [ctypes.POINTER(AttnParams), ctypes.c_void_p]),
     "asuka_b200_attn_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(AttnParams), ctypes.POINTER(ctypes.c_size_t)]),
     "asuka_b200_col_scores": (ctypes.c_int, [ctypes.POINTER(ScoreParams), ctypes.c_void_p]),

@@ -668,6 +668,13 @@ int asuka_b200_device_status(uint32_t* out) {
   return ASUKA_OK;
 }
 
+int asuka_b200_selftest_wait_timeout(uint32_t limit_us, asuka_stream stream) {
+  if (limit_us == 0 || limit_us > 100000) return ASUKA_ERR_BAD_ARGUMENT;
+  const int r = check_arch();
+  if (r != ASUKA_OK) return r;
+  return map_cuda(launch_wait_selftest(static_cast<uint64_t>(limit_us) * 1000ull, static_cast<cudaStream_t>(stream)));
+}
+
 int asuka_b200_attn_fwd(const asuka_attn_params* p, asuka_stream stream) {
   return attn_fwd_impl(p, nullptr, static_cast<cudaStream_t>(stream));
 }

@@ -89,6 +89,8 @@ struct SelectArgs {
 };
 cudaError_t launch_select(const SelectArgs& a, cudaStream_t stream);
 
+// one thread waits `limit_ns` on a barrier nobody completes and records the time-out
+cudaError_t launch_wait_selftest(uint64_t limit_ns, cudaStream_t stream);
 // mean over each group of `group` consecutive heads: [rows * group, S] -> [rows, S]
 cudaError_t launch_group_mean(const float* in, float* out, int rows, int group, int S, cudaStream_t stream);
 // moving average over the key axis of [rows, S] scores (odd kernel size, zero padding)

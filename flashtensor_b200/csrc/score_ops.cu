@@ -4,12 +4,29 @@
 // padding=kernel_size/2, stride=1) along the key axis (cases/kernels/snapkv.py:35-38): a zero-padded
 // moving sum divided by kernel_size (padding counts towards the divisor, PyTorch's default).
 #include "kernels.h"
+#include "sm100_ptx.cuh"
 //
 // gather_kv: KV-cache compaction after a selection, k_out[b, n, h, :] = k[b, idx[b, h, n], h, :]
 // (and v alike): 256-byte rows moved with 16-byte loads and stores, 16 lanes per row.
 
 namespace asuka {
 namespace {
+
+// Self-test of the time-out path every pipeline kernel relies on: one thread waits, through the
+// same bounded wait, on a barrier nothing will ever complete, gives up after `limit_ns` and leaves
+// the same record a stuck pipeline would.  The kernel returns normally and the context stays usable.
+__global__ void wait_selftest_kernel(uint32_t* status, uint64_t limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t abort_s;
+  abort_s = 0;
+  sm100::mbar_init(sm100::smem_u32(&bar), 1);
+  sm100::mbar_fence_init();
+  volatile uint32_t* abortp = &abort_s;
+  if (!sm100::mbar_wait(sm100::smem_u32(&bar), 0, abortp, limit_ns)) {
+    atomicAdd(&status[0], 1u);
+    status[1] = 99;  // site id of the self-test
+  }
+}
 
 __global__ void __launch_bounds__(256) pool_scores_kernel(const float* __restrict__ in,
                                                           float* __restrict__ out, int rows, int S,
@@ -60,6 +77,12 @@ __global__ void __launch_bounds__(256) gather_kv_kernel(GatherArgs a) {
 }
 
 }  // namespace
+
+cudaError_t launch_wait_selftest(uint64_t limit_ns, cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 1, 0, stream>>>(device_status_words(), limit_ns);
+  count_launch();
+  return cudaGetLastError();
+}
 
 cudaError_t launch_gather_kv(const GatherArgs& a, cudaStream_t stream) {
   int bx = (a.n + 15) / 16;

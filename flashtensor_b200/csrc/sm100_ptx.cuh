@@ -78,8 +78,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 #ifndef SM100_WAIT_NS
 #define SM100_WAIT_NS 2000000000ull  // 2 s: three orders of magnitude above any real wait here
 #endif
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint64_t limit_ns = SM100_WAIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
@@ -87,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > SM100_WAIT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1u;
         return false;
       }
@@ -151,6 +151,12 @@ __device__ __forceinline__ void tma_load_4d_hint(uint32_t smem_dst, const CUtens
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
         "r"(c3), "l"(policy)
       : "memory");
+}
+// brings a tile into L2 only (no shared memory, no barrier): a later TMA load of it is an L2 hit
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;

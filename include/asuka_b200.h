@@ -278,6 +278,11 @@ const char* asuka_b200_strerror(int status);
 /* Kernels bound every wait; one that gives up records it in a device-side word.  This reads the
  * word (synchronising the current device) and clears it: 0 = no time-out since the last read. */
 int asuka_b200_device_status(uint32_t* out);
+/* Self-test of that path: launches one thread that waits `limit_us` microseconds (1 .. 100000)
+ * on a barrier nothing completes, through the same bounded wait the pipeline kernels use.  The
+ * kernel gives up, records the time-out and returns; the next asuka_b200_device_status then
+ * reports ASUKA_ERR_DEVICE_TIMEOUT with count 1 and site 99, and the device stays usable. */
+int asuka_b200_selftest_wait_timeout(uint32_t limit_us, asuka_stream stream);
 /* Number of kernels this library has launched in this process (for launch accounting). */
 uint64_t asuka_b200_launch_count(void);
 

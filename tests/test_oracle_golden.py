@@ -132,6 +132,23 @@ def test_seeded_noise_generator():
   assert not np.array_equal(w, O.keyformer_seeded_bits(4, 1, 2, 64, 128))
   assert np.array_equal(w, O.keyformer_seeded_bits(3, 1, 2, 64, 128))
   assert np.array_equal(O.keyformer_seeded_bits(3, 1, 2, 64, 128, units=[1])[0], w[0, 1])   # one unit alone
+  # known answers of the mixer and of the word of a logit (computed once from the definition in
+  # the oracle's docstring and frozen here; the kernels are compared with the oracle on the GPU)
+  assert [int(O.hash_u32(np.uint32(x))) for x in (1, 2, 0xDEADBEEF, 0xFFFFFFFF)] == \
+      [0x688990C0, 0xD1132181, 0xE628C683, 0x6768824A]
+  kat = O.keyformer_seeded_bits(0x123456789ABCDEF, 2, 3, 4, 8)
+  assert kat[1, 2, 3, :4].tolist() == [1103299651, 1057166858, 2759986128, 2888210570]
+  assert kat[0, 0, 0, :2].tolist() == [6164005, 4144588518]
+  # uniform bytes (chi-square, 255 degrees of freedom: mean 255, sigma 22.6) and no visible
+  # correlation between the noise of neighbouring keys or neighbouring query rows
+  big = O.keyformer_seeded_bits(7, 1, 1, 1024, 1024)[0, 0]
+  n = big.size
+  for byte in (big >> np.uint32(24), big & np.uint32(255)):
+    cnt = np.bincount(byte.ravel(), minlength=256)
+    assert ((cnt - n / 256) ** 2 / (n / 256)).sum() < 255 + 5 * 22.6
+  u = ((big >> np.uint32(9)).astype(np.float64) + 0.5) * 2.0 ** -23
+  assert abs(np.corrcoef(u[:, :-1].ravel(), u[:, 1:].ravel())[0, 1]) < 0.01
+  assert abs(np.corrcoef(u[:-1].ravel(), u[1:].ravel())[0, 1]) < 0.01
   er = O.keyformer_seeded_exp_rand(3, 2, 2, 256, 256)
   assert er.shape == (2, 2, 256, 256) and torch.all(er > 0) and torch.isfinite(er).all()
   g = -er.double().log()                                   # Gumbel(0,1): mean 0.5772, var pi^2/6

@@ -629,6 +629,29 @@ def test_roco_mean_and_std_outputs(ops, causal):
   no_timeouts(ops)
 
 
+def test_an_expired_wait_is_reported_and_leaves_the_device_usable(ops):
+  # a wait that nothing will ever satisfy, with a 2 ms limit: the kernel gives up and returns, the
+  # status read reports the time-out once and clears it, and the next call works
+  import ctypes
+  from flashtensor_b200 import _lib
+  lib = _lib.load()
+  no_timeouts(ops)
+  stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+  assert lib.asuka_b200_selftest_wait_timeout(2000, stream) == 0
+  w = (ctypes.c_uint32 * 2)()
+  assert lib.asuka_b200_device_status(w) == -9          # ASUKA_ERR_DEVICE_TIMEOUT
+  assert (w[0], w[1]) == (1, 99)
+  with pytest.raises(_lib.AsukaError, match="DEVICE_TIMEOUT"):
+    lib.asuka_b200_selftest_wait_timeout(1000, stream)
+    ops.device_status()
+  no_timeouts(ops)                                      # cleared by the read
+  assert lib.asuka_b200_selftest_wait_timeout(0, stream) == -10
+  q = torch.randn(1, 256, 2, 128, device="cuda").half()
+  out = ops.attn_fwd(q, q, q)
+  torch.cuda.synchronize()
+  assert torch.isfinite(out.float()).all()
+
+
 # ------------------------------------------------------------------------------------------
 # (3) full benchmark sizes: size-independent properties
 # ------------------------------------------------------------------------------------------
