@@ -1066,24 +1066,6 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           tma_load_4d_hint(sQ + st * kTileBytes, &map_q, bar, 0, h, s0, b, evict_first);
           tma_load_4d_hint(sQ + st * kTileBytes + kHalfBytes, &map_q, bar, 64, h, s0, b, evict_first);
         }
-#ifndef ASUKA_SIMA_PREFETCH_STEPS
-#define ASUKA_SIMA_PREFETCH_STEPS 4
-#endif
-        // This phase reads only L2 and writes; meanwhile the head of the next unit's slab is pulled
-        // into L2, so that its first phase starts on hits while DRAM is already on the tiles behind
-        const int un = u + p.n_groups;
-        if (un < p.n_units) {
-          const int bn = un / p.H, hn = un % p.H;
-          for (int i = 0; i < ASUKA_SIMA_PREFETCH_STEPS && i < nstep; ++i) {
-            const int s0 = tile0 * kTile + i * kRows1;
-            tma_prefetch_l2_4d(&map_k64, 0, hn, s0, bn);
-            tma_prefetch_l2_4d(&map_k64, 64, hn, s0, bn);
-            tma_prefetch_l2_4d(&map_v64, 0, hn, s0, bn);
-            tma_prefetch_l2_4d(&map_v64, 64, hn, s0, bn);
-            tma_prefetch_l2_4d(&map_q64, 0, hn, s0, bn);
-            tma_prefetch_l2_4d(&map_q64, 64, hn, s0, bn);
-          }
-        }
       }
     } else if (warp == 1) {
       constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;

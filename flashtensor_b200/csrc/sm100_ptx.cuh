@@ -152,12 +152,6 @@ __device__ __forceinline__ void tma_load_4d_hint(uint32_t smem_dst, const CUtens
         "r"(c3), "l"(policy)
       : "memory");
 }
-// brings a tile into L2 only (no shared memory, no barrier): a later TMA load of it is an L2 hit
-__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-               : "memory");
-}
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
