@@ -40,8 +40,11 @@ constexpr int kTile = 128;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
 constexpr int kQStages = 4;
-constexpr int kThreads = 640;      // 4 utility warps + 16 key warps
-// 640 threads x 96 registers at launch; no role needs more, so no setmaxnreg here
+#ifndef ASUKA_COL_UTIL_WARPS
+#define ASUKA_COL_UTIL_WARPS 2
+#endif
+constexpr int kUtilWarps = ASUKA_COL_UTIL_WARPS;  // producer and MMA issuer (no idle warps: their registers go to the key warps)
+constexpr int kThreads = (kUtilWarps + 16) * 32;  // + 16 key warps; 576 threads x 112 registers, no setmaxnreg
 constexpr uint32_t kSmemBytes = (2 + kQStages) * kTileBytes + 1024;
 
 struct ColParams {
@@ -347,13 +350,13 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         __syncwarp();
       }
     }
-  } else if (warp < 4) {
+  } else if (warp < kUtilWarps) {
   } else {
     // ------------------------------------------------------------------ one thread per (key, query half)
-    const int kw = warp - 4;
+    const int kw = warp - kUtilWarps;
     const int t = kw >> 3;         // key tile
     const int hq = (kw >> 2) & 1;  // which 64 queries of every query tile
-    const int wq = kw & 3;         // TMEM lane quarter this warp may touch
+    const int wq = warp & 3;       // TMEM lane quarter this warp may touch (every four consecutive key warps cover all four)
     const int key = kv0[t] + wq * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float scale = p.scale_log2;
@@ -509,8 +512,8 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     __syncwarp();
     tmem_dealloc(tbase, 512);
   }
-  if (warp >= 4 && ((warp - 4) >> 2 & 1) == 0 && !*abortp) {
-    const int t = (warp - 4) >> 3;
+  if (warp >= kUtilWarps && ((warp - kUtilWarps) >> 2 & 1) == 0 && !*abortp) {
+    const int t = (warp - kUtilWarps) >> 3;
     const int k_in_tile = (warp & 3) * 32 + lane;
     const int key = kv0[t] + k_in_tile;
     if (key < p.Skv) {  // (implies that this key tile is active)
