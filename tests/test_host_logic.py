@@ -243,3 +243,34 @@ def test_case_bookkeeping_like_the_reference_kernel_object():
   assert kf.get_mem_size(4, 2048, 2048) == 4 * 4 * 2048 * 32 * 128 + 4 * 32 * 2048 * 2048 + 4 * 32 * 2048
   args = ft.H2O(head_num=4, kv_head_num=2).prepare_dummy_inputs(2, 16, 24, device="cpu")
   assert [tuple(a.shape) for a in args] == [(2, 16, 4, 128), (2, 24, 2, 128), (2, 24, 2, 128)]
+
+
+def test_new_entry_points_validate_before_touching_a_device(built_lib):
+  # RoCo statistics outputs, the optional split scratch queries and the wait self-test: every check
+  # below fails on the host, before a device is asked anything
+  lib = _lib.load()
+  score = _t((1, 2, 512), dtype=_lib.F32)
+  sel = lambda **kw: lib.asuka_b200_select_topk(ctypes.byref(_lib.SelectParams(
+      score, score, _t((1, 2, 64), dtype=_lib.I32), 64, 0, kw.get("q_len", 512), 2, kw.get("all_rows", 0),
+      kw.get("mean", _lib.Tensor()), kw.get("std", _lib.Tensor()))), None)
+  assert sel(mean=_t((1, 2, 500), dtype=_lib.F32)) == -3            # statistics have the scores' shape
+  assert sel(std=_t((1, 2, 512), dtype=_lib.I32)) == -2
+  assert sel(q_len=600) == -10                                      # more query rows than keys, causal count
+  need = ctypes.c_size_t(0)
+  assert lib.asuka_b200_attn_workspace_bytes(None, ctypes.byref(need)) == -1
+  assert lib.asuka_b200_attn_workspace_bytes(ctypes.byref(_attn(q=_t((1, 256, 2, 64)))), ctypes.byref(need)) == -3
+  assert lib.asuka_b200_col_scores_workspace_bytes(None, ctypes.byref(need)) == -1
+  assert lib.asuka_b200_case_workspace_bytes_split(None, ctypes.byref(need)) == -1
+  assert lib.asuka_b200_selftest_wait_timeout(0, None) == -10
+  assert lib.asuka_b200_selftest_wait_timeout(200000, None) == -10
+
+
+def test_both_benchmark_arms_print_the_same_config():
+  import bench
+  for case in ("h2o", "roco", "sima"):
+    for world in (1, 8):
+      a = bench.config_of(case, bench.WORKLOADS[case], world, "strong")
+      b = bench.config_of(case, bench.WORKLOADS[case], world, "strong")
+      assert a == b and set(a) == {"workload", "global_batch", "per_gpu_units", "parallelism", "l2"}
+  assert bench.config_of("h2o", bench.WORKLOADS["h2o"], 8, "strong")["per_gpu_units"] == 4
+  assert bench.config_of("h2o", bench.WORKLOADS["h2o"], 8, "weak")["global_batch"] == 8
