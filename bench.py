@@ -226,7 +226,7 @@ def build_step(case, w):
     return lambda q, k, v, er: m.select(q, k, v, er, w["k_keep"])
   if case == "keyformer_seeded":
     m = ft.KeyFormer(tau=w["tau"], head_num=H, kv_head_num=H)
-    return lambda q, k, v: m.seeded(q, k, v, w["seed"], w["k_keep"])
+    return lambda q, k, v: m.seeded(q, k, v, w["seed"], w["k_keep"], unit_offset=w.get("unit_offset", 0))
   m = (ft.EA if case == "ea" else ft.SimA)(head_num=H, kv_head_num=H)
   return lambda q, k, v: (m(q, k, v),)
 
@@ -448,7 +448,7 @@ def main():
     lo, hi = sharding.unit_range(units, rank, world)
     whole = scaling == "weak" or world == 1
     n_local = units if whole else hi - lo
-    ww = w if whole else dict(w, H=n_local)
+    ww = w if whole else dict(w, H=n_local, unit_offset=lo)   # (the seeded noise is keyed by the global unit index)
     step = build_step(args.case, ww)
     set_bytes = input_set_bytes(args.case, w, n_local)
     n_sets = n_input_sets(set_bytes)
@@ -509,7 +509,7 @@ def main():
   # ---- the split against the unsplit run: every rank's outputs are the same bits as its units of
   # ---- the whole configuration computed on one GPU (not timed)
   shard_check = None
-  if world > 1 and args.scaling == "strong" and args.case != "keyformer_seeded":
+  if world > 1 and args.scaling == "strong":
     full = local_inputs(1000, True)
     outs_full = build_step(args.case, w)(*full)
     outs_mine = main_mode["step"](*main_mode["sets"][0])

@@ -37,7 +37,8 @@ class ScoreParams(ctypes.Structure):
   _fields_ = [("q", Tensor), ("k", Tensor), ("lse", Tensor), ("score", Tensor), ("score_sq", Tensor),
               ("exp_rand", Tensor), ("softmax_scale", ctypes.c_float), ("tau", ctypes.c_float),
               ("seed", ctypes.c_uint64), ("causal", ctypes.c_int32), ("mode", ctypes.c_int32),
-              ("corm_mask", Tensor), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64)]
+              ("corm_mask", Tensor), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
+              ("seed_unit_offset", ctypes.c_uint32)]
 
 
 class SelectParams(ctypes.Structure):
@@ -63,7 +64,7 @@ class CaseParams(ctypes.Structure):
               ("score_sq", Tensor), ("exp_rand", Tensor), ("idx", Tensor),
               ("softmax_scale", ctypes.c_float), ("tau", ctypes.c_float), ("seed", ctypes.c_uint64),
               ("causal", ctypes.c_int32), ("k_keep", ctypes.c_int32), ("recent", ctypes.c_int32),
-              ("roco_mean", Tensor), ("roco_std", Tensor)]
+              ("roco_mean", Tensor), ("roco_std", Tensor), ("seed_unit_offset", ctypes.c_uint32)]
 
 
 class AsukaError(RuntimeError):

@@ -201,11 +201,14 @@ class KeyFormer(_Case):
     self._check(q)
     return ops.keyformer(q, k, v, exp_rand, tau=self.tau, causal=self.causal, k_keep=k_keep)
 
-  def seeded(self, q, k, v, seed, k_keep=0):
+  def seeded(self, q, k, v, seed, k_keep=0, unit_offset=0):
     """(out, kf_score[, idx]) with Gumbel(0,1) noise generated inside the kernels from `seed`
-    (the UNIT_GUMBEL generator op of bench/keyformer.mlir:17) instead of an `exp_rand` operand."""
+    (the UNIT_GUMBEL generator op of bench/keyformer.mlir:17) instead of an `exp_rand` operand.
+    `unit_offset`: index of the first (batch, head) unit of these tensors within the whole problem
+    when they are one GPU's slice of it (flashtensor_b200.sharding.unit_range)."""
     self._check(q)
-    return ops.keyformer(q, k, v, None, tau=self.tau, seed=seed, causal=self.causal, k_keep=k_keep)
+    return ops.keyformer(q, k, v, None, tau=self.tau, seed=seed, causal=self.causal, k_keep=k_keep,
+                         unit_offset=unit_offset)
 
   def prepare(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):
     ret = super().prepare(batch_size, q_len, kv_len, dtype, device)

@@ -279,6 +279,7 @@ int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a)
     if (!(p->tau > 0.f) || std::isinf(p->tau)) return ASUKA_ERR_BAD_ARGUMENT;
     a->tau = p->tau;
     a->seed = p->seed;
+    a->unit_offset = p->seed_unit_offset;
     if (p->exp_rand.ptr != nullptr) {
       if ((r = check_er(p->exp_rand, c->s)) != ASUKA_OK) return r;
       a->exp_rand = static_cast<const float*>(p->exp_rand.ptr);
@@ -497,6 +498,7 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
   sp.softmax_scale = p->softmax_scale;
   sp.tau = p->tau;
   sp.seed = p->seed;
+  sp.seed_unit_offset = p->seed_unit_offset;
   sp.causal = p->causal;
   sp.mode = kind == CASE_H2O ? ASUKA_SCORE_SUM : kind == CASE_ROCO ? ASUKA_SCORE_SUM_SQ : ASUKA_SCORE_PERTURBED;
   if (kind == CASE_KF) sp.lse.ptr = lse_kf;

@@ -60,6 +60,7 @@ struct ColParams {
   const float* exp_rand;
   int64_t er_sb, er_sh, er_sq;
   uint64_t seed;
+  uint32_t unit_off;  // added to the (batch * H + head) index the seeded noise is keyed by
   uint32_t* status;
   int chained;        // the kernel ahead in the stream does not write q or k
   // Query-range split, for launches with too few key blocks to fill the SMs: the query tiles are
@@ -363,7 +364,7 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     float acc2[4] = {0.f, 0.f, 0.f, 0.f};
     bool ok = true;
-    const uint32_t head_key = kMode == 3 ? seeded_head_key(p.seed, static_cast<uint32_t>(bh)) : 0u;
+    const uint32_t head_key = kMode == 3 ? seeded_head_key(p.seed, static_cast<uint32_t>(bh) + p.unit_off) : 0u;
     const float* er_col = nullptr;
     if constexpr (kMode == 2 || kMode == 4) {  // mode 4: the threshold operand, strides 0 for b and h
       er_col = p.exp_rand + static_cast<int64_t>(b) * p.er_sb + static_cast<int64_t>(h) * p.er_sh +
@@ -685,7 +686,7 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                                       : p.exp_rand + static_cast<int64_t>(b) * p.er_sb +
                                             static_cast<int64_t>(h) * p.er_sh +
                                             static_cast<int64_t>(min(row, p.Sq - 1)) * p.er_sq;
-    const uint32_t head_key = kNoise == 2 ? seeded_head_key(p.seed, static_cast<uint32_t>(bh)) : 0u;
+    const uint32_t head_key = kNoise == 2 ? seeded_head_key(p.seed, static_cast<uint32_t>(bh) + p.unit_off) : 0u;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
@@ -817,6 +818,7 @@ ColParams make_params(const ScoreArgs& a, const AttnShape& s) {
   p.er_sh = a.er_stride_h;
   p.er_sq = a.er_stride_q;
   p.seed = a.seed;
+  p.unit_off = a.unit_offset;
   p.status = device_status_words();
   p.chained = a.chained;
   p.q_chunk = p.nq_tiles;

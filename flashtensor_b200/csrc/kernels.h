@@ -64,6 +64,7 @@ struct ScoreArgs {
   int64_t er_stride_b, er_stride_h, er_stride_q;  // elements (innermost stride 1)
   float tau;
   uint64_t seed;
+  uint32_t unit_offset;    // seeded noise: index of this call's first (batch, head) unit in the whole problem
   int mode;                // asuka_score_mode
   int chained;             // 1: the kernel ahead in the stream is this library's own and writes none of
                            // q and k, so the K tiles may be fetched before that kernel has finished

@@ -865,6 +865,7 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   // role advances them the same way (ntile is the same for every unit of this CTA).
   uint32_t n1 = 0, n2 = 0, nu = 0;  // phase-1 steps, phase-2 tiles, units done so far
   int prev_u = -1;
+  int pre2 = 0;  // (producer thread) phase-2 tiles already requested during phase 1's tail
   bool ok = true;
   const int nstep = ntile * (kTile / kRows1);  // phase-1 steps of 64 rows
 
@@ -890,6 +891,29 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           tma_load_4d_hint(base + kSubBytes + kSubHalf, &map_v64, bar, 64, h, s0, b, evict_first);
           tma_load_4d_hint(base + 2 * kSubBytes, &map_q64, bar, 0, h, s0, b, evict_last);
           tma_load_4d_hint(base + 2 * kSubBytes + kSubHalf, &map_q64, bar, 64, h, s0, b, evict_last);
+        }
+        // Once every stage of this unit has been consumed (by the MMA and by the column sums) the
+        // first Q tiles of phase 2 are requested at once, so that they arrive while the group
+        // barrier and the reduce run; the rest follow in phase 2 proper.
+        bool drained = true;
+        for (int i = max(0, nstep - kSt); i < nstep && drained; ++i) {
+          const uint32_t k = n1 + i;
+          drained = mbar_wait(smem_u32(&bars.empty[k % kSt]), (k / kSt) & 1, abortp);
+        }
+        pre2 = 0;
+        if (drained) {
+          for (int i = 0; i < ntile && i < kQ; ++i, ++pre2) {
+            const uint32_t k = n2 + i;
+            const int st = k % kQ;
+            if (k >= kQ && !mbar_wait(smem_u32(&bars.q_empty[st]), (k / kQ - 1) & 1, abortp)) break;
+            const uint32_t bar = smem_u32(&bars.q_full[st]);
+            const int s0 = (tile0 + ntile - 1 - i) * kTile;
+            mbar_expect_tx(bar, kTileBytes);
+            tma_load_4d_hint(sQ + st * kTileBytes, &map_q, bar, 0, h, s0, b, evict_first);
+            tma_load_4d_hint(sQ + st * kTileBytes + kHalfBytes, &map_q, bar, 64, h, s0, b, evict_first);
+          }
+        } else {
+          record_timeout(p.status, 60);
         }
       }
     } else if (warp == 1) {
@@ -1053,7 +1077,7 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------------------------ phase 2
     if (warp == 0) {
       if (lane == 0) {
-        for (int i = 0; i < ntile; ++i) {
+        for (int i = pre2; i < ntile; ++i) {
           const uint32_t k = n2 + i;
           const int st = k % kQ;
           if (k >= kQ && !mbar_wait(smem_u32(&bars.q_empty[st]), (k / kQ - 1) & 1, abortp)) {

@@ -100,7 +100,7 @@ def attn_fwd(q, k, v, causal=True, softmax_scale=0.0, return_lse=False, out=None
 
 
 def col_scores(q, k, lse, mode=_lib.SCORE_SUM, causal=True, softmax_scale=0.0, exp_rand=None,
-               tau=1.0, seed=0, corm_mask=None):
+               tau=1.0, seed=0, corm_mask=None, unit_offset=0):
   """Per-key reductions over the query rows of the attention probabilities: [B,H,Skv] f32 sums
   (and sums of squares in mode SCORE_SUM_SQ); in mode SCORE_CORM a bool tensor that is True where
   some probability reaches its threshold in `corm_mask` [Sq, Skv]."""
@@ -114,7 +114,7 @@ def col_scores(q, k, lse, mode=_lib.SCORE_SUM, causal=True, softmax_scale=0.0, e
     score_sq = torch.empty_like(score) if mode == _lib.SCORE_SUM_SQ else None
     p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _desc(score), _desc(score_sq),
                          _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
-                         int(bool(causal)), int(mode), _desc(corm_mask), None, 0)
+                         int(bool(causal)), int(mode), _desc(corm_mask), None, 0, int(unit_offset))
     ws = _scratch(lib.asuka_b200_col_scores_workspace_bytes, "asuka_b200_col_scores_workspace_bytes", p, q4.device)
     if ws is not None:
       p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
@@ -122,7 +122,7 @@ def col_scores(q, k, lse, mode=_lib.SCORE_SUM, causal=True, softmax_scale=0.0, e
   return (score, score_sq) if score_sq is not None else score
 
 
-def keyformer_rowstat(q, k, causal=True, softmax_scale=0.0, exp_rand=None, tau=1.5, seed=0):
+def keyformer_rowstat(q, k, causal=True, softmax_scale=0.0, exp_rand=None, tau=1.5, seed=0, unit_offset=0):
   """Base-2 log-sum-exp per query row of the perturbed logits (s + g) / tau: [B,H,Sq] f32."""
   lib = _lib.load()
   q4, k4 = _as4d(q), _as4d(k)
@@ -131,7 +131,7 @@ def keyformer_rowstat(q, k, causal=True, softmax_scale=0.0, exp_rand=None, tau=1
     lse = torch.empty((q4.shape[0], q4.shape[2], q4.shape[1]), dtype=torch.float32, device=q4.device)
     p = _lib.ScoreParams(_desc(q4), _desc(k4), _desc(lse), _lib.Tensor(), _lib.Tensor(),
                          _desc(exp_rand), float(softmax_scale), float(tau), int(seed),
-                         int(bool(causal)), _lib.SCORE_PERTURBED, _lib.Tensor())
+                         int(bool(causal)), _lib.SCORE_PERTURBED, _lib.Tensor(), None, 0, int(unit_offset))
     _lib.check("asuka_b200_keyformer_rowstat",
                lib.asuka_b200_keyformer_rowstat(ctypes.byref(p), _stream(q4)))
   return lse
@@ -221,7 +221,7 @@ def linattn32_fwd(q, k, v, ea=False, out=None):
 
 def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None, tau=1.0, seed=0,
           k_keep=0, recent=0, n_idx=0, workspace=None, out=None, score=None, score_sq=None, idx=None,
-          roco_mean=None, roco_std=None):
+          roco_mean=None, roco_std=None, unit_offset=0):
   lib = _lib.load()
   q4, k4, v4 = _as4d(q), _as4d(k), _as4d(v)
   _same_device(q4, k4, v4, exp_rand)
@@ -240,7 +240,7 @@ def _case(fn_name, q, k, v, causal, softmax_scale, want_sq=False, exp_rand=None,
     p = _lib.CaseParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(score),
                         _desc(score_sq), _desc(exp_rand), _desc(idx), float(softmax_scale),
                         float(tau), int(seed), int(bool(causal)), int(k_keep), int(recent),
-                        _desc(roco_mean), _desc(roco_std))
+                        _desc(roco_mean), _desc(roco_std), int(unit_offset))
     if workspace is None:
       nbytes = ctypes.c_size_t(0)
       _lib.check("asuka_b200_case_workspace_bytes_split",
@@ -275,7 +275,7 @@ def h2o_static(q, k, v, out, score, idx=None, causal=True, softmax_scale=0.0, k_
   with _on(q4.device):
     p = _lib.CaseParams(_desc(q4), _desc(k4), _desc(v4), _desc(_as4d(out)), _desc(score),
                         _lib.Tensor(), _lib.Tensor(), _desc(idx), float(softmax_scale), 1.0, 0,
-                        int(bool(causal)), int(k_keep), int(recent), _lib.Tensor(), _lib.Tensor())
+                        int(bool(causal)), int(k_keep), int(recent), _lib.Tensor(), _lib.Tensor(), 0)
     _lib.check("asuka_b200_h2o_static", lib.asuka_b200_h2o_static(ctypes.byref(p), _stream(q4)))
   return (out, score, idx) if idx is not None else (out, score)
 
@@ -298,7 +298,9 @@ def roco(q, k, v, causal=True, softmax_scale=0.0, k_keep=0, return_stats=False, 
 
 def keyformer(q, k, v, exp_rand=None, tau=1.5, seed=0, causal=True, softmax_scale=0.0, k_keep=0,
               **buffers):
-  """(out, kf_score[, idx]) -- cases/kernels/kf.py:19-42; exp_rand=None uses the seeded noise."""
+  """(out, kf_score[, idx]) -- cases/kernels/kf.py:19-42; exp_rand=None uses the seeded noise
+  (`unit_offset`: index of this call's first (batch, head) unit when it is a slice of a larger
+  problem, so that the slice gets the noise the whole problem would have had)."""
   out, score, _, idx = _case("asuka_b200_keyformer", q, k, v, causal, softmax_scale,
                              exp_rand=exp_rand, tau=tau, seed=seed, k_keep=k_keep, n_idx=k_keep,
                              **buffers)

@@ -120,6 +120,10 @@ typedef struct {
                              head) units the query rows are divided over several CTAs per key block,
                              whose partial sums are parked here and added in a fixed order */
   uint64_t workspace_bytes;
+  uint32_t seed_unit_offset; /* seeded noise: the noise of unit (b, h) is keyed by seed_unit_offset +
+                                b * H + h.  A caller that holds a slice of the (batch, head) units of
+                                a larger problem passes the index of its first unit and gets the
+                                noise the whole problem would have had; 0 otherwise */
 } asuka_score_params;
 
 int asuka_b200_col_scores(const asuka_score_params* p, asuka_stream stream);
@@ -229,6 +233,7 @@ typedef struct {
   int32_t recent;
   asuka_tensor roco_mean; /* RoCo with idx only, optional: per-key mean of the probabilities over the */
   asuka_tensor roco_std;  /* rows that attend to the key, and their standard deviation; [B, H, Skv] f32 */
+  uint32_t seed_unit_offset; /* Keyformer with seeded noise: as in asuka_score_params */
 } asuka_case_params;
 
 int asuka_b200_case_workspace_bytes(const asuka_case_params* p, size_t* bytes);

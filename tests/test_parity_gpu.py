@@ -629,6 +629,27 @@ def test_roco_mean_and_std_outputs(ops, causal):
   no_timeouts(ops)
 
 
+def test_a_slice_of_the_units_reproduces_the_whole_problem(ops):
+  # one GPU's share of a problem split by (batch, head): same outputs as the units of the unsplit
+  # run, including the seeded Keyformer noise, which is keyed by the unit's index in the whole problem
+  import flashtensor_b200 as ft
+  from flashtensor_b200 import sharding
+  B, S, H, seed, k_keep = 2, 640, 6, 77, 80
+  q, k, v = (t.cuda() for t in O.make_inputs("attn", B, S, S, H, 128, torch.float16, seed=8))
+  whole = ft.KeyFormer(tau=1.5, head_num=H, kv_head_num=H).seeded(q, k, v, seed, k_keep)
+  world = 4
+  for rank in range(world):
+    lo, hi = sharding.unit_range(B * H, rank, world)
+    qs, ks, vs = (sharding.shard_bshd(t, rank, world) for t in (q, k, v))
+    part = ft.KeyFormer(tau=1.5, head_num=hi - lo, kv_head_num=hi - lo).seeded(qs, ks, vs, seed, k_keep, unit_offset=lo)
+    assert torch.equal(part[0], sharding.shard_bshd(whole[0], rank, world))
+    assert torch.equal(part[1], sharding.shard_bhs(whole[1], rank, world))
+    assert torch.equal(part[2], sharding.shard_bhs(whole[2], rank, world))
+  parts = [ft.H2O(head_num=3, kv_head_num=3)(*(sharding.shard_bshd(t, r, world) for t in (q, k, v)))[1] for r in range(world)]
+  assert torch.equal(sharding.gather_units(parts, B, H), ft.H2O(head_num=H, kv_head_num=H)(q, k, v)[1])
+  no_timeouts(ops)
+
+
 def test_an_expired_wait_is_reported_and_leaves_the_device_usable(ops):
   # a wait that nothing will ever satisfy, with a 2 ms limit: the kernel gives up and returns, the
   # status read reports the time-out once and clears it, and the next call works
