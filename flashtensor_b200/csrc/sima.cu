@@ -832,7 +832,7 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars.acc_full[i]), 1);
-      mbar_init(smem_u32(&bars.acc_empty[i]), 128);
+      mbar_init(smem_u32(&bars.acc_empty[i]), 256);
     }
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -1116,8 +1116,12 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         __syncwarp();
       }
-    } else if (warp >= 4 && warp < 8) {
+    } else if (warp >= 4) {
+      // Eight epilogue warps: two per TMEM lane quarter, each with half of the 128 output columns
+      // (four warps alone finish a tile in about 1.5 us, which held this phase to half of the
+      // SM's share of the memory bandwidth).
       const int wq = warp & 3;
+      const int ch0 = ((warp - 4) >> 2) * 2;  // this warp's two chunks of 32 columns: 0,1 or 2,3
       const int r = wq * 32 + lane;
       const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
       const float inv4[4] = {inv4_s[0], inv4_s[1], inv4_s[2], inv4_s[3]};
@@ -1132,10 +1136,10 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if constexpr (!kOutF32) {
           if (tid == 128) tma_store_wait_read_n<1>();
         }
-        named_bar_sync(1, 128);
+        named_bar_sync(1, 256);
         uint8_t* stage = smem_gen + (sO - smem_base) + (kOutF32 ? 0 : buf * kTileBytes);
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int cc = ch0; cc < ch0 + 2; ++cc) {
           uint32_t uu[32];
           tmem_ld32(tAcc + lane_base + buf * 128 + cc * 32, uu);
           tmem_wait_ld();
@@ -1176,8 +1180,8 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bars.acc_empty[buf]));
         if constexpr (kOutF32) {
-          named_bar_sync(1, 128);
-          for (int rr = wq; rr < kTile; rr += 4) {
+          named_bar_sync(1, 256);
+          for (int rr = warp - 4; rr < kTile; rr += 8) {
             const int srow = s0 + rr;
             if (srow < p.S) {
               const float4 v = *reinterpret_cast<const float4*>(stage + rr * 512 + (lane << 4));
@@ -1189,7 +1193,7 @@ sima_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           }
         } else {
           fence_proxy_async_smem();
-          named_bar_sync(1, 128);
+          named_bar_sync(1, 256);
           if (tid == 128) {
 #ifdef ASUKA_SIMA_STORE_PLAIN
             tma_store_4d(&map_o, sO + buf * kTileBytes, 0, h, s0, b);
@@ -1255,6 +1259,7 @@ Plan make_plan(const SimaShape& s) {
 }  // namespace
 
 size_t sima_workspace_bytes(const SimaShape& s) { return make_plan(s).total; }
+
 
 cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                         const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
