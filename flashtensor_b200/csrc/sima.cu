@@ -1269,13 +1269,13 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   const Plan pl = make_plan(s);
   const int bh = s.B * s.H;
   uint8_t* w = static_cast<uint8_t*>(ws);
-  // One persistent kernel for all three steps when there are enough units to keep every group of
-  // four CTAs busy for a few rounds (and the partial slots fit the workspace plan above).
+  // One persistent kernel for all three steps when there are enough units to keep most groups of
+  // four CTAs busy (and the partial slots fit the workspace plan above).
   const int n_groups = num_sms / kFuGroup;
 #ifdef ASUKA_SIMA_NO_FUSED
   const bool fused = false;
 #else
-  const bool fused = !s.ea && maps64 != nullptr && n_groups > 0 && bh >= 2 * n_groups && pl.ntiles >= kFuGroup &&
+  const bool fused = !s.ea && maps64 != nullptr && n_groups > 0 && 2 * bh >= n_groups && pl.ntiles >= kFuGroup &&
                      static_cast<long long>(bh) * pl.nchunks >= static_cast<long long>(n_groups) * kFuGroup;
 #endif
   if (fused) {
@@ -1296,7 +1296,8 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
       // a unit costs a CTA five passes over its slab (K, V, Q in; Q again from L2; out) at its
       // share of the memory bandwidth, about 44 bytes per nanosecond per SM on this part
       const double unit_ns = static_cast<double>(fp.tiles_per_cta) * kTile * 128 * 2 * 5 / 44.0;
-      fp.stagger_ns = static_cast<uint32_t>(0.4 * unit_ns);
+      // (with fewer than three rounds of units the head start costs more than it brings)
+      fp.stagger_ns = bh >= 3 * n_groups ? static_cast<uint32_t>(0.4 * unit_ns) : 0u;
     }
     cudaError_t e = cudaMemsetAsync(fp.arrive, 0, static_cast<size_t>(bh) * 2 * sizeof(uint32_t), stream);
     if (e != cudaSuccess) return e;
