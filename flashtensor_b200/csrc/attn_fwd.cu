@@ -55,6 +55,7 @@ struct FwdParams {
   float* lse2;
   void* out;                 // [B, Sq, H, 128], 16-bit, strides in elements
   int64_t o_sb, o_ss, o_sh;
+  int out_vec32;             // every output row starts on a 32-byte boundary: 256-bit stores
   uint32_t* status;
   // Key-range split, for launches with fewer work items than SMs can share evenly: the keys of
   // every item are dealt out to `parts` items of `ceil(n / parts)` key tiles each.  A query tile
@@ -76,6 +77,14 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 256-bit store: one instruction per 32-byte sector instead of two (the epilogue's stores go to 32
+// different rows per warp instruction, so the number of instructions is what the LSU pays for)
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&r)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -631,8 +640,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           if (row < p.Sq) {
 #pragma unroll
-            for (int g = 0; g < 8; ++g)
-              *reinterpret_cast<uint4*>(orow + c * 32 + g * 4) = make_uint4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t w[8] = {o[g * 8], o[g * 8 + 1], o[g * 8 + 2], o[g * 8 + 3],
+                                     o[g * 8 + 4], o[g * 8 + 5], o[g * 8 + 6], o[g * 8 + 7]};
+              st_global_v8(orow + c * 32 + g * 8, w);  // (the workspace rows are 512-byte aligned)
+            }
           }
         }
         if (row < p.Sq)
@@ -652,14 +664,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             mbar_arrive(smem_u32(&bars.o_free[t]));
           }
           if (row < p.Sq) {
+            uint32_t w[16];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 v;
-              v.x = pack2<kBF16>(__uint_as_float(o[g * 8 + 0]) * inv_l, __uint_as_float(o[g * 8 + 1]) * inv_l);
-              v.y = pack2<kBF16>(__uint_as_float(o[g * 8 + 2]) * inv_l, __uint_as_float(o[g * 8 + 3]) * inv_l);
-              v.z = pack2<kBF16>(__uint_as_float(o[g * 8 + 4]) * inv_l, __uint_as_float(o[g * 8 + 5]) * inv_l);
-              v.w = pack2<kBF16>(__uint_as_float(o[g * 8 + 6]) * inv_l, __uint_as_float(o[g * 8 + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+            for (int g = 0; g < 16; ++g)
+              w[g] = pack2<kBF16>(__uint_as_float(o[2 * g]) * inv_l, __uint_as_float(o[2 * g + 1]) * inv_l);
+            if (p.out_vec32) {
+              st_global_v8(orow + c * 32, *reinterpret_cast<const uint32_t(*)[8]>(&w[0]));
+              st_global_v8(orow + c * 32 + 16, *reinterpret_cast<const uint32_t(*)[8]>(&w[8]));
+            } else {
+#pragma unroll
+              for (int g = 0; g < 4; ++g)
+                *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
             }
           }
         }
@@ -801,6 +816,7 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.o_sb = o_sb;
   p.o_ss = o_ss;
   p.o_sh = o_sh;
+  p.out_vec32 = (reinterpret_cast<uintptr_t>(out) % 32 == 0 && o_sb % 16 == 0 && o_ss % 16 == 0 && o_sh % 16 == 0) ? 1 : 0;
   p.status = device_status_words();
   p.part_o = static_cast<float*>(split_ws);
   p.part_ml = p.part_o + static_cast<size_t>(s.B) * s.H * s.Sq * p.parts * 128;

@@ -387,6 +387,12 @@ def test_layouts_strided_and_2d(ops):
   out, score = ops.h2o(*views)
   close(out, ref_out, "strided out")
   close(score, ref_score, "strided score")
+  # an output that starts on a 16-byte but not a 32-byte boundary (the epilogue's narrower stores)
+  flat = torch.zeros(B * S * H * 128 + 8, dtype=torch.float16, device="cuda")
+  odd = flat[8:].view(B, S, H, 128)
+  assert odd.data_ptr() % 32 == 16
+  ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), out=odd)
+  assert torch.equal(odd, ops.attn_fwd(q.cuda(), k.cuda(), v.cuda()))
   q2, k2, v2 = (t[0].reshape(S, H * 128).cuda() for t in (q, k, v))
   out2 = ops.attn_fwd(q2, k2, v2)
   assert out2.shape == (S, H * 128)
