@@ -20,6 +20,13 @@ NVCC_FLAGS = [
 ]
 
 
+def _flags():
+  """The fixed flags plus whatever ASUKA_NVCC_FLAGS adds (e.g. -DASUKA_TUNE_ENV, which lets the
+  environment variables ASUKA_FWD_PARTS / ASUKA_COL_CHUNKS force the work-item split factors for
+  tuning runs)."""
+  return NVCC_FLAGS + os.environ.get("ASUKA_NVCC_FLAGS", "").split()
+
+
 def _nvcc():
   for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
     if cand and os.path.exists(cand):
@@ -45,7 +52,7 @@ def build(force=False, verbose=False):
     objs.append(obj)
     stale = force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), dep_mtime)
     if stale:
-      cmd = [nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj]
+      cmd = [nvcc] + _flags() + ["-c", src, "-o", obj]
       res = subprocess.run(cmd, capture_output=True, text=True)
       log = res.stdout + res.stderr
       with open(obj + ".log", "w") as f:

@@ -2,7 +2,7 @@
 
 Run once where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports the reference's own eager modules (cases/kernels/{attn,h2o,kf,roco,gemma2,snapkv,corm}.py),
 unmodified,
@@ -136,4 +136,6 @@ def make_gqa(ref_root):
 
 
 if __name__ == "__main__":
-  main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+  if len(sys.argv) != 2:
+    raise SystemExit("usage: python tests/golden/make_golden.py <path to the reference checkout>")
+  main(sys.argv[1])
