@@ -133,6 +133,36 @@ def test_attn_and_h2o_vs_oracle(ops, shape, dtype):
   no_timeouts(ops)
 
 
+@pytest.mark.parametrize("shape", [(1, 4100, 4100, 2, True), (1, 3000, 5000, 3, True), (1, 4200, 4200, 2, False),
+                                   (2, 4096, 4096, 1, True)])
+def test_long_sequences_with_few_heads_vs_oracle(ops, shape):
+  # few (batch, head) units and long sequences: the forward kernel divides every work item's key
+  # range over several CTAs (partial results merged in part order) and the column pass divides the
+  # query rows (partial sums added in range order); ragged, rectangular and unmasked shapes
+  B, Sq, Skv, H, causal = shape
+  dtype = torch.bfloat16 if H == 3 else torch.float16
+  q, k, v = O.make_inputs("roco", B, Sq, Skv, H, 128, dtype, seed=Sq)
+  ref_out, ref_sum, ref_sq = O.roco(q, k, v, causal)
+  qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+  out, lse = ops.attn_fwd(qd, kd, vd, causal=causal, return_lse=True)
+  out2, ssum, ssq = ops.roco(qd, kd, vd, causal=causal)
+  torch.cuda.synchronize()
+  close(out, ref_out, "out")
+  assert torch.equal(out, out2)
+  close(ssum, ref_sum, "roco_score")
+  close(ssq, ref_sq, "roco_sq_score")
+  torch.testing.assert_close(ssum.sum(-1).cpu(), torch.full((B, H), float(Sq)), rtol=1e-4, atol=1e-2)
+  # the row statistic the forward kernel returns is the base-2 log-sum-exp of the scaled logits
+  s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) / 128 ** 0.5
+  if causal:
+    s = s + torch.triu(torch.full((Sq, Skv), float("-inf")), diagonal=Skv - Sq + 1)
+  torch.testing.assert_close(lse.cpu(), torch.logsumexp(s, -1) * 1.4426950408889634, rtol=1e-4, atol=2e-3)
+  # run-to-run identical, whatever order the parts finish in
+  assert torch.equal(out, ops.attn_fwd(qd, kd, vd, causal=causal))
+  assert torch.equal(ssum, ops.roco(qd, kd, vd, causal=causal)[1])
+  no_timeouts(ops)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 384, 384, 2), (2, 1000, 1000, 3), (1, 200, 456, 2)])
 def test_roco_vs_oracle(ops, shape, dtype):
