@@ -298,7 +298,7 @@ int prep_scores(const asuka_score_params* p, bool rowstat, QKV* c, ScoreArgs* a)
 
 // `chained`: the kernel ahead in the stream is one of this library's that writes neither q nor k
 int col_scores_impl(const asuka_score_params* p, cudaStream_t stream, bool chained = false, void* ws = nullptr,
-                    size_t ws_bytes = 0) {
+                    size_t ws_bytes = 0, PendingChunkSum* pending = nullptr) {
   QKV c;
   ScoreArgs a;
   int r = prep_scores(p, false, &c, &a);
@@ -311,7 +311,7 @@ int col_scores_impl(const asuka_score_params* p, cudaStream_t stream, bool chain
   size_t usable = 0;
   void* split_ws = align_ws(ws != nullptr ? ws : p->workspace, ws != nullptr ? ws_bytes : p->workspace_bytes, &usable);
   const int chunks = col_scores_chunks(c.s, a.mode, sms, usable);
-  return map_cuda(launch_col_scores(mq, mk, a, c.s, split_ws, chunks, stream));
+  return map_cuda(launch_col_scores(mq, mk, a, c.s, split_ws, chunks, stream, pending));
 }
 
 int kf_rowstat_impl(const asuka_score_params* p, cudaStream_t stream) {
@@ -327,7 +327,7 @@ int kf_rowstat_impl(const asuka_score_params* p, cudaStream_t stream) {
 constexpr int kSelectMaxS32 = 32768;  // 4-byte keys in shared memory
 constexpr int kSelectMaxS64 = 16384;  // 8-byte keys (RoCo)
 
-int select_impl(const asuka_select_params* p, cudaStream_t stream) {
+int select_impl(const asuka_select_params* p, cudaStream_t stream, const PendingChunkSum* pending = nullptr) {
   if (p == nullptr) return ASUKA_ERR_NULL_POINTER;
   if (p->score.ptr == nullptr || p->idx.ptr == nullptr) return ASUKA_ERR_NULL_POINTER;
   if (p->mode != ASUKA_SELECT_TOPK && p->mode != ASUKA_SELECT_TOPK_RECENT && p->mode != ASUKA_SELECT_ROCO)
@@ -365,6 +365,9 @@ int select_impl(const asuka_select_params* p, cudaStream_t stream) {
   a.all_rows = roco && p->all_rows ? 1 : 0;
   a.mean = roco ? static_cast<float*>(p->mean.ptr) : nullptr;
   a.std = roco ? static_cast<float*>(p->std.ptr) : nullptr;
+  a.part = pending != nullptr ? pending->part : nullptr;
+  a.part_sq = pending != nullptr ? pending->part_sq : nullptr;
+  a.n_chunks = pending != nullptr ? pending->n_chunks : 0;
   return map_cuda(launch_select(a, stream));
 }
 
@@ -592,13 +595,18 @@ int case_impl(const asuka_case_params* p, CaseKind kind, void* ws, size_t ws_byt
   if (kind == CASE_KF) {
     if ((r = kf_rowstat_impl(&sp, stream)) != ASUKA_OK) return r;
   }
-  if ((r = col_scores_impl(&sp, stream, true, col_ws, col_bytes)) != ASUKA_OK) return r;
+  // with a selection to follow (and no group mean in between) the selection kernel adds the column
+  // pass's partial sums itself: one launch fewer
+  PendingChunkSum pending;
+  pending.n_chunks = 0;
+  if ((r = col_scores_impl(&sp, stream, true, col_ws, col_bytes, want_idx && !gqa ? &pending : nullptr)) != ASUKA_OK)
+    return r;
   if (gqa) {
     r = map_cuda(launch_group_mean(head_scores, static_cast<float*>(p->score.ptr), static_cast<int>(B * Hkv),
                                    static_cast<int>(H / Hkv), static_cast<int>(p->k.shape[1]), stream));
     if (r != ASUKA_OK) return r;
   }
-  if (want_idx) r = select_impl(&lp, stream);
+  if (want_idx) r = select_impl(&lp, stream, pending.n_chunks > 0 ? &pending : nullptr);
   return r;
 }
 

@@ -858,8 +858,10 @@ size_t col_scores_split_bytes(const AttnShape& s, int mode, int chunks) {
 }
 
 cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
-                              const AttnShape& s, void* split_ws, int chunks, cudaStream_t stream) {
+                              const AttnShape& s, void* split_ws, int chunks, cudaStream_t stream,
+                              PendingChunkSum* pending) {
   ColParams p = make_params(a, s);
+  if (pending != nullptr) pending->n_chunks = 0;
   if (chunks > 1 && split_ws != nullptr && a.mode != ASUKA_SCORE_CORM) {
     p.q_chunk = (p.nq_tiles + chunks - 1) / chunks;
     p.n_qchunks = (p.nq_tiles + p.q_chunk - 1) / p.q_chunk;
@@ -881,6 +883,12 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
   if (e != cudaSuccess || p.n_qchunks == 1) return e;
   const size_t n = static_cast<size_t>(s.B) * s.H * s.Skv;
   const bool sq = a.mode == ASUKA_SCORE_SUM_SQ;
+  if (pending != nullptr) {  // the caller's next kernel adds the partial sums
+    pending->part = p.part;
+    pending->part_sq = sq ? p.part_sq : nullptr;
+    pending->n_chunks = p.n_qchunks;
+    return e;
+  }
   e = launch_dependent(sum_chunks_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, stream,
                        static_cast<const float*>(p.part), static_cast<const float*>(sq ? p.part_sq : nullptr),
                        a.score, a.score_sq, p.n_qchunks, n);

@@ -71,8 +71,16 @@ struct ScoreArgs {
 };
 // `split_ws` / `chunks`: optional query-range split (see col_scores_chunks); chunks = 1 or a null
 // workspace gives every key block one CTA that walks all query tiles.
+// `pending`: when non-null and the query-range split is active, the final sum of the partial
+// results is left to the caller (the selection kernel can do it on its way in) and described here.
+struct PendingChunkSum {
+  const float* part;     // [n_chunks][rows * S]
+  const float* part_sq;  // or null
+  int n_chunks;          // 0: nothing pending, the scores are final
+};
 cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, const ScoreArgs& a,
-                              const AttnShape& s, void* split_ws, int chunks, cudaStream_t stream);
+                              const AttnShape& s, void* split_ws, int chunks, cudaStream_t stream,
+                              PendingChunkSum* pending = nullptr);
 int col_scores_chunks(const AttnShape& s, int mode, int num_sms, size_t ws_bytes);
 size_t col_scores_split_bytes(const AttnShape& s, int mode, int chunks);
 // Keyformer row statistic: writes lse2' [B,H,Sq] of (s + g) / tau
@@ -85,6 +93,11 @@ struct SelectArgs {
   int32_t* idx;           // [B*H, n_out]
   int rows, S, k_keep, recent, q_len, mode;
   int all_rows;           // RoCo: every key is seen by all q_len rows (unmasked attention)
+  // partial sums of a query-range split still to be added (in range order) into score / score_sq,
+  // which the kernel then also writes; n_chunks = 0: the scores are final
+  const float* part;
+  const float* part_sq;
+  int n_chunks;
   float* mean;            // RoCo, optional outputs [B*H, S]
   float* std;
 };

@@ -72,6 +72,22 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const SelectArgs
   // (launched as a programmatic dependent: the scores are the output of the kernel ahead)
   sm100::griddep_wait();
   sm100::griddep_launch_dependents();
+  if (a.n_chunks > 0) {
+    // the column pass left partial sums per query range: add them in range order and write the
+    // scores (every thread later reads back only what it wrote itself: same stride)
+    const size_t n = static_cast<size_t>(a.rows) * a.S, off = static_cast<size_t>(row) * a.S;
+    float* sw = const_cast<float*>(srow);
+    float* qw = const_cast<float*>(qrow);
+    for (int j = tid; j < a.S; j += kSelThreads) {
+      float s1 = 0.f, s2 = 0.f;
+      for (int c = 0; c < a.n_chunks; ++c) {
+        s1 += a.part[c * n + off + j];
+        if (a.part_sq != nullptr) s2 += a.part_sq[c * n + off + j];
+      }
+      sw[j] = s1;
+      if (a.part_sq != nullptr) qw[j] = s2;
+    }
+  }
   for (int j = tid; j < ncand; j += kSelThreads) keys[j] = make_key<KeyT>(a, srow, qrow, j);
   hist[tid] = 0;
   hist[tid + kSelThreads] = 0;
