@@ -274,3 +274,40 @@ def test_both_benchmark_arms_print_the_same_config():
       assert a == b and set(a) == {"workload", "global_batch", "per_gpu_units", "parallelism", "l2"}
   assert bench.config_of("h2o", bench.WORKLOADS["h2o"], 8, "strong")["per_gpu_units"] == 4
   assert bench.config_of("h2o", bench.WORKLOADS["h2o"], 8, "weak")["global_batch"] == 8
+
+
+def test_ctypes_structures_match_the_c_header(tmp_path):
+  # the header is the contract; the Python binding restates every parameter block: compile a C
+  # program against the header that prints sizes and field offsets, and compare
+  import os
+  import shutil
+  import subprocess
+  cc = shutil.which("gcc") or shutil.which("cc")
+  if cc is None:
+    pytest.skip("no C compiler")
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  blocks = {
+      "asuka_tensor": (_lib.Tensor, ["ptr", "dtype", "ndim", "shape", "stride"]),
+      "asuka_attn_params": (_lib.AttnParams, ["q", "lse", "softmax_scale", "causal", "softcap", "workspace", "workspace_bytes"]),
+      "asuka_score_params": (_lib.ScoreParams, ["lse", "exp_rand", "tau", "seed", "mode", "corm_mask", "workspace", "seed_unit_offset"]),
+      "asuka_select_params": (_lib.SelectParams, ["idx", "k_keep", "q_len", "mode", "all_rows", "mean", "std"]),
+      "asuka_sima_params": (_lib.SimaParams, ["q", "out"]),
+      "asuka_linattn32_params": (_lib.LinAttn32Params, ["out", "ea"]),
+      "asuka_gather_params": (_lib.GatherParams, ["idx", "v_out"]),
+      "asuka_case_params": (_lib.CaseParams, ["idx", "softmax_scale", "seed", "recent", "roco_mean", "roco_std", "seed_unit_offset"]),
+  }
+  lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "asuka_b200.h"', "int main(void) {"]
+  for name, (_, fields) in blocks.items():
+    lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
+    for f in fields:
+      lines.append(f'  printf("{name}.{f} %zu\\n", offsetof({name}, {f}));')
+  lines += ["  return 0;", "}"]
+  src = tmp_path / "layout.c"
+  src.write_text("\n".join(lines))
+  exe = tmp_path / "layout"
+  subprocess.run([cc, "-I", os.path.join(root, "include"), str(src), "-o", str(exe)], check=True)
+  got = dict(l.split() for l in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+  for name, (cls, fields) in blocks.items():
+    assert int(got[name]) == ctypes.sizeof(cls), name
+    for f in fields:
+      assert int(got[f"{name}.{f}"]) == getattr(cls, f).offset, f"{name}.{f}"
