@@ -43,7 +43,6 @@ struct SimaWs {
   float* part_c;     // [BH][nchunks][2][128] partial ck, cq
   uint16_t* m16;     // [BH][e][d] scaled M'^T in the input type
   float* inv_scale;  // [BH][4]: one per block of 32 output channels
-  float* part_cmax;  // [BH][nchunks][128] EA only: partial column maxima of K over the sequence
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -121,47 +120,41 @@ __device__ __forceinline__ uint4 pack8(float (&f)[8]) {
   }
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
+template <bool kBF16>
+__device__ __forceinline__ float2 unpack2_16(uint32_t w) {
+  if constexpr (kBF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <bool kBF16>
+__device__ __forceinline__ uint32_t pack2_16(float2 f) {
+  if constexpr (kBF16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(f.x, f.y);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(f.x, f.y);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+// element-wise maximum of two packed pairs of 16-bit values
+template <bool kBF16>
+__device__ __forceinline__ uint32_t max2_16(uint32_t a, uint32_t b) {
+  if constexpr (kBF16) {
+    __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  } else {
+    __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+}
+// EA: of the four pairs of exponentials per 16-byte chunk, how many go to the FMA pipe
+#ifndef ASUKA_EA_POLY_PAIRS
+#define ASUKA_EA_POLY_PAIRS 0
+#endif
+constexpr int kEaPolyPairs = ASUKA_EA_POLY_PAIRS;
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-// ---------------------------------------------------------------------------------------------
-// 0. (EA only) column maxima of K over a slab of the sequence: softmax over the sequence axis
-//    (bench/ea.mlir:14) needs them before any exponential is taken.  Plain coalesced 16-byte
-//    loads; one partial per slab, reduced by the statistics kernel.
-// ---------------------------------------------------------------------------------------------
-template <bool kBF16>
-__global__ void __launch_bounds__(256, 4) ea_colmax_kernel(const StatsParams p) {
-  __shared__ float red[16][kTile];
-  const int tid = threadIdx.x;
-  const int chunk = static_cast<int>(blockIdx.x) % p.nchunks;
-  const int bh = static_cast<int>(blockIdx.x) / p.nchunks;
-  const int b = bh / p.H, h = bh % p.H;
-  const int chunk16 = tid & 15, rg = tid >> 4;
-  const int row0 = chunk * p.tiles_per_chunk * kTile;
-  const int row1 = min(p.S, row0 + p.tiles_per_chunk * kTile);
-  const uint16_t* base = p.k + static_cast<int64_t>(b) * p.k_sb + static_cast<int64_t>(h) * p.k_sh + chunk16 * 8;
-  float mx[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
-  for (int r = row0 + rg; r < row1; r += 16) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + static_cast<int64_t>(r) * p.k_ss));
-    float f[8];
-    unpack8<kBF16>(v, f);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) mx[i] = fmaxf(mx[i], f[i]);
-  }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) red[rg][chunk16 * 8 + i] = mx[i];
-  __syncthreads();
-  if (tid < kTile) {
-    float m = -INFINITY;
-#pragma unroll
-    for (int g = 0; g < 16; ++g) m = fmaxf(m, red[g][tid]);
-    p.ws.part_cmax[(static_cast<size_t>(bh) * p.nchunks + chunk) * kTile + tid] = m;
-  }
 }
 
 // kEA: the EA program.  K is exponentiated in place in shared memory against the column maxima
@@ -179,6 +172,9 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __shared__ __align__(8) StBars bars;
   __shared__ float red[2][8][kTile];
   __shared__ float cmax_s[kTile];
+  // EA: a block of ones, the B operand of the small MMA that gives the column sums of the
+  // exponentiated K (every element is 1, so its layout does not matter)
+  __shared__ __align__(1024) uint16_t ones_s[kEA ? 1024 : 8];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -203,17 +199,13 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_fence_init();
   }
   if constexpr (kEA) {
-    if (tid >= 128 && tid < 256) {  // column maxima of the whole sequence: reduce every slab's partial
-      const int d = tid - 128;
-      const float* pc = p.ws.part_cmax + static_cast<size_t>(blockIdx.x / p.nchunks) * p.nchunks * kTile + d;
-      float m = -INFINITY;
-      for (int c = 0; c < p.nchunks; ++c) m = fmaxf(m, pc[c * kTile]);
-      cmax_s[d] = m;
-    }
+    for (int i = tid; i < 1024; i += kStThreads) ones_s[i] = kBF16 ? 0x3F80 : 0x3C00;
+    fence_proxy_async_smem();
   }
+  constexpr uint32_t kTmemCols = kEA ? 256 : 128;  // EA: columns 128.. hold the column sums
   if (warp == 1) {
     __syncwarp();
-    tmem_alloc(smem_u32(&tmem_base_s), 128);
+    tmem_alloc(smem_u32(&tmem_base_s), kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -221,13 +213,98 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
 
+  // EA, pass A: the column maxima of this slab of K, which the exponentials of pass B are taken
+  // against (the reduce brings the slabs to a common reference).  K runs through the same stage
+  // ring, two tiles per stage (the V half holds the second one); its second read in pass B comes
+  // from L2.  `ring0` = ring positions used by pass A.
+  const int ring0 = kEA ? (ntile + 1) / 2 : 0;
+  if constexpr (kEA) {
+    if (warp == 0) {
+      if (lane == 0) {
+        const uint64_t keep = l2_policy_evict_last();  // pass B reads everything for the last time
+        for (int j = 0; j < ring0; ++j) {
+          const int st = j % kSt;
+          if (j >= kSt && !mbar_wait(smem_u32(&bars.empty[st]), (j / kSt - 1) & 1, abortp)) {
+            record_timeout(p.status, 46);
+            break;
+          }
+          const uint32_t bar = smem_u32(&bars.full[st]);
+          const uint32_t base = smem_base + st * kStageBytes;
+          const int nt = min(2, ntile - 2 * j);
+          mbar_expect_tx(bar, nt * kTileBytes);
+          for (int t = 0; t < nt; ++t) {
+            const int s0 = (tile0 + 2 * j + t) * kTile;
+            tma_load_4d_hint(base + t * kTileBytes, &map_k, bar, 0, h, s0, b, keep);
+            tma_load_4d_hint(base + t * kTileBytes + kHalfBytes, &map_k, bar, 64, h, s0, b, keep);
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // no MMA in this pass: the warp stands in for the arrival its commit gives in pass B
+      for (int j = 0; j < ring0; ++j) {
+        const int st = j % kSt;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (j / kSt) & 1, abortp))) {
+          if (lane == 0) record_timeout(p.status, 47);
+          break;
+        }
+        if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
+        __syncwarp();
+      }
+    } else if (warp >= 4) {
+      const int which = (warp - 4) >> 2;
+      const int t128 = tid - 128 - which * 128;
+      const int chunk16 = t128 & 15;
+      const int rg16 = which * 8 + (t128 >> 4);
+      uint32_t mxp[4];  // running maxima, packed as loaded (the maximum of 16-bit values is exact)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) mxp[e] = kBF16 ? 0xFF80FF80u : 0xFC00FC00u;  // -inf, -inf
+      for (int j = 0; j < ring0; ++j) {
+        const int st = j % kSt;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (j / kSt) & 1, abortp))) {
+          if (lane == 0) record_timeout(p.status, 48);
+          break;
+        }
+        const int nt = min(2, ntile - 2 * j);
+        for (int t = 0; t < nt; ++t) {
+          const uint8_t* tile = smem_gen + st * kStageBytes + t * kTileBytes + (chunk16 >> 3) * kHalfBytes;
+          const int s0 = (tile0 + 2 * j + t) * kTile;
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int row = rg16 + 16 * r;
+            const uint4 v = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
+            if (s0 + row < p.S) {  // (rows past the sequence were zero-filled by the load)
+              mxp[0] = max2_16<kBF16>(mxp[0], v.x);
+              mxp[1] = max2_16<kBF16>(mxp[1], v.y);
+              mxp[2] = max2_16<kBF16>(mxp[2], v.z);
+              mxp[3] = max2_16<kBF16>(mxp[3], v.w);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
+      }
+      float mx[8];
+      unpack8<kBF16>(make_uint4(mxp[0], mxp[1], mxp[2], mxp[3]), mx);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red[which][t128 >> 4][chunk16 * 8 + e] = mx[e];
+      named_bar_sync(1, 256);
+      if (which == 0) {
+        float m = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) m = fmaxf(m, fmaxf(red[0][g][t128], red[1][g][t128]));
+        cmax_s[t128] = m;
+      }
+      named_bar_sync(1, 256);  // cmax_s complete
+    }
+  }
+
   // stage layout: [K | V | Q] tiles
   if (warp == 0) {
     if (lane == 0) {
       for (int i = 0; i < ntile; ++i) {
-        const int st = i % kSt;
-        const uint32_t use = static_cast<uint32_t>(i / kSt);
-        if (use > 0 && !mbar_wait(smem_u32(&bars.empty[st]), (use - 1) & 1, abortp)) {
+        const int k = ring0 + i;
+        const int st = k % kSt;
+        if (k >= kSt && !mbar_wait(smem_u32(&bars.empty[st]), (k / kSt - 1) & 1, abortp)) {
           record_timeout(p.status, 41);
           break;
         }
@@ -235,10 +312,18 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t base = smem_base + st * kStageBytes;
         const int s0 = (tile0 + i) * kTile;
         mbar_expect_tx(bar, (kEA ? 2 : 3) * kTileBytes);
-        tma_load_4d(base, &map_k, bar, 0, h, s0, b);
-        tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h, s0, b);
-        tma_load_4d(base + kTileBytes, &map_v, bar, 0, h, s0, b);
-        tma_load_4d(base + kTileBytes + kHalfBytes, &map_v, bar, 64, h, s0, b);
+        if constexpr (kEA) {
+          const uint64_t drop = l2_policy_evict_first();
+          tma_load_4d_hint(base, &map_k, bar, 0, h, s0, b, drop);
+          tma_load_4d_hint(base + kHalfBytes, &map_k, bar, 64, h, s0, b, drop);
+          tma_load_4d_hint(base + kTileBytes, &map_v, bar, 0, h, s0, b, drop);
+          tma_load_4d_hint(base + kTileBytes + kHalfBytes, &map_v, bar, 64, h, s0, b, drop);
+        } else {
+          tma_load_4d(base, &map_k, bar, 0, h, s0, b);
+          tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h, s0, b);
+          tma_load_4d(base + kTileBytes, &map_v, bar, 0, h, s0, b);
+          tma_load_4d(base + kTileBytes + kHalfBytes, &map_v, bar, 64, h, s0, b);
+        }
         if constexpr (!kEA) {
           tma_load_4d(base + 2 * kTileBytes, &map_q, bar, 0, h, s0, b);
           tma_load_4d(base + 2 * kTileBytes + kHalfBytes, &map_q, bar, 64, h, s0, b);
@@ -252,11 +337,13 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_MN_MAJOR, UMMA_MN_MAJOR, 128, 128);
       bool ok = true;
       for (int i = 0; i < ntile && ok; ++i) {
-        const int st = i % kSt;
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kSt) & 1, abortp));
+        const int k = ring0 + i;
+        const int st = k % kSt;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (k / kSt) & 1, abortp));
         if (!ok) { if (lane == 0) record_timeout(p.status, 42); break; }
         if constexpr (kEA) {
-          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.ktrans[st]), (i / kSt) & 1, abortp));
+          // (pass B is the only user of these barriers: its own step count picks one and gives the parity)
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.ktrans[i % kSt]), (i / kSt) & 1, abortp));
           if (!ok) { if (lane == 0) record_timeout(p.status, 45); break; }
         }
         tc_fence_after_sync();
@@ -269,6 +356,16 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t off = static_cast<uint64_t>(kk * (2048 >> 4));
             umma_ss(tbase, adesc + off, bdesc + off, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          if constexpr (kEA) {
+            // column sums of the exponentiated (and rounded) K: the same A against 16 columns of ones
+            constexpr uint32_t idesc16 = umma_idesc_f16(kFmt, UMMA_MN_MAJOR, UMMA_MN_MAJOR, 128, 16);
+            const uint64_t odesc = umma_smem_desc_sw128(smem_u32(ones_s), 1024, 1024);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t off = static_cast<uint64_t>(kk * (2048 >> 4));
+              umma_ss(tbase + 128, adesc + off, odesc, idesc16, (i > 0 || kk > 0) ? 1u : 0u);
+            }
           }
           umma_commit(smem_u32(&bars.empty[st]));
         }
@@ -284,10 +381,17 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int chunk16 = t128 & 15;   // 8 consecutive channels
     const int rg = t128 >> 4;        // rows rg, rg+8, ...
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const float kL2e = 1.4426950408889634f;
+    float2 ncm[4];  // EA: -(column maximum) * log2(e) of this thread's eight channels
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      ncm[e] = kEA ? make_float2(-cmax_s[chunk16 * 8 + 2 * e] * kL2e, -cmax_s[chunk16 * 8 + 2 * e + 1] * kL2e)
+                   : make_float2(0.f, 0.f);
     bool ok = true;
     for (int i = 0; i < ntile; ++i) {
-      const int st = i % kSt;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kSt) & 1, abortp));
+      const int k = ring0 + i;
+      const int st = k % kSt;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (k / kSt) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 43); break; }
       if constexpr (kEA) {
         // all 256 threads work on the K tile: rows 16 apart per thread; k' = exp(k - colmax),
@@ -295,24 +399,28 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         uint8_t* tile = smem_gen + st * kStageBytes + (chunk16 >> 3) * kHalfBytes;
         const int rg16 = which * 8 + rg;
         const int s0 = (tile0 + i) * kTile;
-        float cm[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) cm[e] = cmax_s[chunk16 * 8 + e] * 1.4426950408889634f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           const int row = rg16 + 16 * r;
           uint4* ptr = reinterpret_cast<uint4*>(tile + sw128_offset(row, chunk16 & 7));
-          float f[8];
-          unpack8<kBF16>(*ptr, f);
-          const bool live = s0 + row < p.S;
+          if (s0 + row < p.S) {
+            const uint4 raw = *ptr;
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            uint32_t o[4];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = live ? ex2_approx(fmaf(f[e], 1.4426950408889634f, -cm[e])) : 0.f;
-          *ptr = pack8<kBF16>(f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] += f[e];
+            for (int e = 0; e < 4; ++e) {
+              const float2 x = __ffma2_rn(unpack2_16<kBF16>(w[e]), make_float2(kL2e, kL2e), ncm[e]);
+              // half of the exponentials on the special-function unit, half on the FMA pipe
+              const float2 y = e < kEaPolyPairs ? ex2_fma_pipe2(x) : make_float2(ex2_approx(x.x), ex2_approx(x.y));
+              o[e] = pack2_16<kBF16>(y);
+            }
+            *ptr = make_uint4(o[0], o[1], o[2], o[3]);
+          } else {
+            *ptr = make_uint4(0u, 0u, 0u, 0u);
+          }
         }
         fence_proxy_async_smem();  // written by ordinary stores, read by the tensor pipe
-        mbar_arrive(smem_u32(&bars.ktrans[st]));
+        mbar_arrive(smem_u32(&bars.ktrans[i % kSt]));
       } else {
         const uint8_t* tile = smem_gen + st * kStageBytes + (which ? 2 * kTileBytes : 0) +
                               (chunk16 >> 3) * kHalfBytes;
@@ -326,16 +434,13 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) red[which][rg][chunk16 * 8 + i] = acc[i];
     if constexpr (kEA) {
-      named_bar_sync(1, 256);
-      float s = 0.f;
-#pragma unroll
-      for (int g = 0; g < 8; ++g) s += red[0][g][t128] + red[1][g][t128];
-      // slot 0: the softmax denominators' partial; slot 1 (SimA's sum|Q|) is not used by EA
-      p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + which) * kTile + t128] = which ? 1.f : s;
+      // slot 1 of the partial (SimA's sum|Q|): the slab's column maxima; slot 0 is written below
+      if (which == 1)
+        p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + 1) * kTile + t128] = cmax_s[t128];
     } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) red[which][rg][chunk16 * 8 + i] = acc[i];
       named_bar_sync(1 + which, 128);
       float s = 0.f;
 #pragma unroll
@@ -361,11 +466,19 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 32; ++i) dst[(c * 32 + i) * kTile + d] = __uint_as_float(u[i]);
           }
+          if constexpr (kEA) {
+            // slot 0: this slab's part of the softmax denominators (relative to the slab's maxima)
+            uint32_t u[16];
+            tmem_ld16(tbase + (static_cast<uint32_t>(wq * 32) << 16) + 128, u);
+            tmem_wait_ld();
+            p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + 0) * kTile + d] = __uint_as_float(u[0]);
+          }
         } else if (lane == 0) {
           record_timeout(p.status, 44);
         }
       } else {
         for (int i = 0; i < 128; ++i) dst[i * kTile + d] = 0.f;
+        if constexpr (kEA) p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + 0) * kTile + d] = 0.f;
       }
     }
   }
@@ -374,7 +487,7 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tbase, 128);
+    tmem_dealloc(tbase, kTmemCols);
   }
 }
 
@@ -385,10 +498,12 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // One CTA per (head, block of 32 output channels e): 4096 entries of M'^T, its own power-of-two
 // scale (the epilogue of step 3 multiplies each 32-column chunk by the matching inverse).
 constexpr int kRedBlocks = 4;
+constexpr int kMaxChunks = 16;  // slabs per (batch, head) in the three-kernel path
 constexpr int kRedElems = kMElems / kRedBlocks;
 template <bool kBF16>
 __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p) {
   __shared__ float inv_c[kTile];
+  __shared__ float w_s[kMaxChunks][kTile];  // EA: exp(slab maximum - maximum), per slab and column
   __shared__ float wmax[8];
   __shared__ float s_scale;
   const int blk = blockIdx.x % kRedBlocks;
@@ -396,12 +511,26 @@ __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p
   const float* pc = p.ws.part_c + static_cast<size_t>(bh) * p.nchunks * 2 * kTile;
   const float* pm = p.ws.part_m + static_cast<size_t>(bh) * p.nchunks * kMElems + blk * kRedElems;
   if (tid < kTile) {
-    float ck = 0.f, cq = 0.f;
-    for (int c = 0; c < p.nchunks; ++c) {
-      ck += pc[(c * 2 + 0) * kTile + tid];
-      cq += pc[(c * 2 + 1) * kTile + tid];
+    if (p.ea) {
+      // each slab's exponentials were taken against the slab's own column maxima (slot 1): bring
+      // them to the maximum over the sequence.  A slab without rows has maximum -inf, weight 0.
+      float m = -INFINITY;
+      for (int c = 0; c < p.nchunks; ++c) m = fmaxf(m, pc[(c * 2 + 1) * kTile + tid]);
+      float ck = 0.f;
+      for (int c = 0; c < p.nchunks; ++c) {
+        const float w = __expf(pc[(c * 2 + 1) * kTile + tid] - m);
+        w_s[c][tid] = w;
+        ck = fmaf(pc[(c * 2 + 0) * kTile + tid], w, ck);
+      }
+      inv_c[tid] = __fdiv_rn(1.0f, ck);
+    } else {
+      float ck = 0.f, cq = 0.f;
+      for (int c = 0; c < p.nchunks; ++c) {
+        ck += pc[(c * 2 + 0) * kTile + tid];
+        cq += pc[(c * 2 + 1) * kTile + tid];
+      }
+      inv_c[tid] = __fdiv_rn(1.0f, __fmul_rn(ck, cq));
     }
-    inv_c[tid] = p.ea ? __fdiv_rn(1.0f, ck) : __fdiv_rn(1.0f, __fmul_rn(ck, cq));
   }
   __syncthreads();
   float vals[kRedElems / 256];
@@ -410,7 +539,11 @@ __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p
   for (int it = 0; it < kRedElems / 256; ++it) {
     const int idx = it * 256 + tid;  // = e_local * 128 + d
     float m = 0.f;
-    for (int c = 0; c < p.nchunks; ++c) m += pm[static_cast<size_t>(c) * kMElems + idx];
+    if (p.ea) {
+      for (int c = 0; c < p.nchunks; ++c) m = fmaf(pm[static_cast<size_t>(c) * kMElems + idx], w_s[c][idx & 127], m);
+    } else {
+      for (int c = 0; c < p.nchunks; ++c) m += pm[static_cast<size_t>(c) * kMElems + idx];
+    }
     m *= inv_c[idx & 127];
     vals[it] = m;
     amax = fmaxf(amax, fabsf(m));
@@ -453,8 +586,14 @@ __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p
 // ---------------------------------------------------------------------------------------------
 // 3. out = (Q M'') * inv_scale
 // ---------------------------------------------------------------------------------------------
-constexpr int kOutThreads = 256;  // warp 0 producer, warp 1 MMA, warps 4-7 epilogue
-constexpr uint32_t kOutSmem = (1 + 4 + 2) * kTileBytes + 1024;  // M'', up to four Q stages, two staging buffers
+constexpr int kOutThreads = 256;  // warp 0 producer, warp 1 MMA, warp 2 stores (16-bit output), warps 4-7 epilogue
+// Q stages.  16-bit output: the epilogue writes a tile's result over the Q tile it came from (the
+// MMA has consumed it by then) and the stage goes back to the producer once the store has read it,
+// so all of shared memory beside M'' is one ring of stages.  f32 output: a 64 KB staging buffer.
+__host__ __device__ constexpr int out_stages(bool out_f32, bool ea) { return out_f32 ? (ea ? 3 : 4) : (ea ? 5 : 6); }
+__host__ __device__ constexpr uint32_t out_smem_bytes(bool out_f32, bool ea) {
+  return (1 + out_stages(out_f32, ea) + (out_f32 ? 2 : 0)) * kTileBytes + 1024;
+}
 
 struct OutParams {
   int B, H, S;
@@ -466,29 +605,32 @@ struct OutParams {
 };
 
 struct OutBars {
-  uint64_t m_full, q_full[4], q_empty[4], acc_full[2], acc_empty[2];
-  uint64_t qtrans[4];  // EA only: the Q tile of the stage has been exponentiated in place
+  uint64_t m_full, q_full[6], q_empty[6], acc_full[2], acc_empty[2];
+  uint64_t qtrans[6];     // EA only: the Q tile of the stage has been exponentiated in place
+  uint64_t out_ready[6];  // 16-bit output: the result tile has been written into the stage
 };
 
-// kEA: softmax over the features of every query row (bench/ea.mlir:13): the row's thread
-// exponentiates it in place in shared memory against the row maximum before the MMA reads it, and
-// divides by the row sum in the epilogue (the same thread owns the row's accumulator lane).
+// kEA: softmax over the features of every query row (bench/ea.mlir:13): eight more warps
+// exponentiate the Q tile in place in shared memory against the row maxima before the MMA reads
+// it; a second, 16-column MMA against a block of ones gives the row sums of exactly the rounded
+// values the first one multiplies, and the epilogue divides by them.
 template <bool kBF16, bool kOutF32, bool kEA>
 __global__ void __launch_bounds__(kOutThreads + (kEA ? 256 : 0), 1)  // EA: warps 8-15 exponentiate Q
 sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_m,
                 const __grid_constant__ CUtensorMap map_o, const OutParams p) {
-  // four Q stages (three in flight) where shared memory allows it; EA's extra state leaves room for three
-  constexpr int kQ = kEA ? 3 : 4;
+  constexpr int kQ = out_stages(kOutF32, kEA);
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) OutBars bars;
-  __shared__ float inv_r_s[kEA ? kQ + 2 : 1][kTile];  // EA: 1 / row sum of the exponentiated Q rows, ring over tiles
+  // EA: a block of ones, the B operand of the small MMA that gives the row sums of the
+  // exponentiated Q (every element is 1, so its layout does not matter)
+  __shared__ __align__(1024) uint16_t ones_s[kEA ? 1024 : 8];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sM = smem_base;
   const uint32_t sQ = smem_base + kTileBytes;
-  const uint32_t sO = sQ + kQ * kTileBytes;  // two 32 KB staging buffers (one 64 KB for f32)
+  const uint32_t sO = sQ + kQ * kTileBytes;  // f32 output only: one 64 KB staging buffer
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile uint32_t* abortp = &abort_s;
@@ -509,12 +651,21 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(smem_u32(&bars.acc_full[i]), 1);
       mbar_init(smem_u32(&bars.acc_empty[i]), 128);
     }
-    for (int i = 0; i < kQ; ++i) mbar_init(smem_u32(&bars.qtrans[i]), 256);
+    for (int i = 0; i < kQ; ++i) {
+      mbar_init(smem_u32(&bars.qtrans[i]), 256);
+      mbar_init(smem_u32(&bars.out_ready[i]), 128);
+    }
     mbar_fence_init();
   }
+  if constexpr (kEA) {
+    for (int i = tid; i < 1024; i += kOutThreads + 256) ones_s[i] = kBF16 ? 0x3F80 : 0x3C00;
+    fence_proxy_async_smem();
+  }
+  // two accumulators of 128 columns; EA: columns 256.. and 272.. hold the row sums of the two
+  constexpr uint32_t kTmemCols = kEA ? 512 : 256;
   if (warp == 1) {
     __syncwarp();
-    tmem_alloc(smem_u32(&tmem_base_s), 256);
+    tmem_alloc(smem_u32(&tmem_base_s), kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -574,19 +725,48 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
             umma_ss(tbase + buf * 128, qdesc + off, mdesc + off, idesc, kk > 0 ? 1u : 0u);
           }
+          if constexpr (kEA) {
+            // row sums of the exponentiated (and rounded) Q: the same A against 16 columns of ones
+            constexpr uint32_t idesc16 = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 16);
+            const uint64_t odesc = umma_smem_desc_sw128(smem_u32(ones_s), 1024, 1024);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+              umma_ss(tbase + 256 + buf * 16, qdesc + off, odesc, idesc16, kk > 0 ? 1u : 0u);
+            }
+          }
           umma_commit(smem_u32(&bars.acc_full[buf]));
-          umma_commit(smem_u32(&bars.q_empty[st]));
+          if constexpr (kOutF32) umma_commit(smem_u32(&bars.q_empty[st]));  // (else: the store warp releases it)
         }
         __syncwarp();
       }
     }
+  } else if (!kOutF32 && warp == 2) {
+    // ---------------------------------------------------------------- 16-bit output: store warp
+    if (lane == 0) {
+      for (int i = 0; i < ntile; ++i) {
+        const int st = i % kQ;
+        if (!mbar_wait(smem_u32(&bars.out_ready[st]), (i / kQ) & 1, abortp)) {
+          record_timeout(p.status, 58);
+          break;
+        }
+        const int s0 = (tile0 + i) * kTile;
+        tma_store_4d(&map_o, sQ + st * kTileBytes, 0, h, s0, b);
+        tma_store_4d(&map_o, sQ + st * kTileBytes + kHalfBytes, 64, h, s0, b);
+        tma_store_commit();
+        tma_store_wait_read();  // the stage may be overwritten from here on
+        mbar_arrive(smem_u32(&bars.q_empty[st]));
+      }
+      tma_store_wait_all();
+    }
   } else if (kEA && warp >= 8) {
     // ------------------------------------------------------------- EA: softmax numerators of Q
     // Two threads per row (adjacent lanes, 64 features each) exponentiate every Q tile in place
-    // against the row maximum and leave 1 / (sum of the rounded values) for the epilogue thread
-    // of the row.  Two warps per scheduler: one alone issues an ex2 only every ~11 clk.
+    // against the row maximum; the row sums come from the tensor pipe (above).  Half of the
+    // exponentials run on the special-function unit, half on the FMA pipe.
     const int t256 = tid - 256;
     const int r = t256 >> 1, half = t256 & 1;
+    const float kL2e = 1.4426950408889634f;
     bool ok = true;
     for (int i = 0; i < ntile && ok; ++i) {
       const int st = i % kQ;
@@ -594,33 +774,28 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!ok) { if (lane == 0) record_timeout(p.status, 57); break; }
       uint8_t* tile = smem_gen + (sQ - smem_base) + st * kTileBytes + half * kHalfBytes;
       uint4 raw[8];
-      float mx = -INFINITY;
+      uint32_t mxp = kBF16 ? 0xFF80FF80u : 0xFC00FC00u;  // (-inf, -inf); the maximum of 16-bit values is exact
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         raw[c] = *reinterpret_cast<const uint4*>(tile + sw128_offset(r, c));
-        float f[8];
-        unpack8<kBF16>(raw[c], f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) mx = fmaxf(mx, f[e]);
+        mxp = max2_16<kBF16>(mxp, max2_16<kBF16>(max2_16<kBF16>(raw[c].x, raw[c].y), max2_16<kBF16>(raw[c].z, raw[c].w)));
       }
+      const float2 m2 = unpack2_16<kBF16>(mxp);
+      float mx = fmaxf(m2.x, m2.y);
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      const float neg = -mx * 1.4426950408889634f;
-      float sum = 0.f;
+      const float2 neg = make_float2(-mx * kL2e, -mx * kL2e);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        float f[8];
-        unpack8<kBF16>(raw[c], f);
+        const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+        uint32_t o[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = ex2_approx(fmaf(f[e], 1.4426950408889634f, neg));
-        *reinterpret_cast<uint4*>(tile + sw128_offset(r, c)) = pack8<kBF16>(f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sum += f[e];
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __ffma2_rn(unpack2_16<kBF16>(w[e]), make_float2(kL2e, kL2e), neg);
+          const float2 y = e < kEaPolyPairs ? ex2_fma_pipe2(x) : make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          o[e] = pack2_16<kBF16>(y);
+        }
+        *reinterpret_cast<uint4*>(tile + sw128_offset(r, c)) = make_uint4(o[0], o[1], o[2], o[3]);
       }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      // The slot last held tile i - 5.  This tile's Q landed only after the MMA of tile i - 3 had
-      // retired, that MMA was issued only after the epilogue of tile i - 5 had released its
-      // accumulator, and the epilogue reads its 1/sum before it does that.
-      if (half == 0) inv_r_s[i % (kQ + 2)][r] = 1.f / sum;
       fence_proxy_async_smem();  // the tile was written by ordinary stores, the tensor pipe reads it
       mbar_arrive(smem_u32(&bars.qtrans[st]));
     }
@@ -638,13 +813,17 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_full[buf]), (i >> 1) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 55); break; }
       tc_fence_after_sync();
-      const float inv_r = kEA ? inv_r_s[i % (kQ + 2)][r] : 1.f;
-      // the staging buffer about to be overwritten must have been read by its previous store
-      if constexpr (!kOutF32) {
-        if (tid == 128) tma_store_wait_read_n<1>();
+      float inv_r = 1.f;
+      if constexpr (kEA) {
+        uint32_t u[16];
+        tmem_ld16(tbase + lane_base + 256 + buf * 16, u);
+        tmem_wait_ld();
+        inv_r = 1.f / __uint_as_float(u[0]);
       }
-      named_bar_sync(1, 128);
-      uint8_t* stage = smem_gen + (sO - smem_base) + (kOutF32 ? 0 : buf * kTileBytes);
+      // f32: the staging buffer is free again once the previous tile's copy-out has passed the
+      // barrier; 16-bit: the result goes over the Q tile of this stage, which the MMA has consumed
+      if constexpr (kOutF32) named_bar_sync(1, 128);
+      uint8_t* stage = smem_gen + (kOutF32 ? (sO - smem_base) : (sQ - smem_base) + (i % kQ) * kTileBytes);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t u[32];
@@ -701,16 +880,8 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       } else {
         fence_proxy_async_smem();
-        named_bar_sync(1, 128);
-        if (tid == 128) {
-          tma_store_4d(&map_o, sO + buf * kTileBytes, 0, h, s0, b);
-          tma_store_4d(&map_o, sO + buf * kTileBytes + kHalfBytes, 64, h, s0, b);
-          tma_store_commit();
-        }
+        mbar_arrive(smem_u32(&bars.out_ready[i % kQ]));
       }
-    }
-    if constexpr (!kOutF32) {
-      if (tid == 128) tma_store_wait_read();
     }
   }
 
@@ -718,7 +889,7 @@ sima_out_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tbase, 256);
+    tmem_dealloc(tbase, kTmemCols);
   }
 }
 
@@ -1232,7 +1403,7 @@ size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 struct Plan {
   int ntiles, nchunks, tiles_per_chunk;
-  size_t off_pm, off_pc, off_m16, off_sc, off_cmax, off_cnt, total;
+  size_t off_pm, off_pc, off_m16, off_sc, off_cnt, total;
 };
 
 Plan make_plan(const SimaShape& s) {
@@ -1241,7 +1412,7 @@ Plan make_plan(const SimaShape& s) {
   pl.ntiles = (s.S + kTile - 1) / kTile;
   int want = (1024 + bh - 1) / bh;
   if (want < 1) want = 1;
-  if (want > 16) want = 16;
+  if (want > kMaxChunks) want = kMaxChunks;
   if (want > pl.ntiles) want = pl.ntiles;
   pl.tiles_per_chunk = (pl.ntiles + want - 1) / want;
   pl.nchunks = (pl.ntiles + pl.tiles_per_chunk - 1) / pl.tiles_per_chunk;
@@ -1250,7 +1421,6 @@ Plan make_plan(const SimaShape& s) {
   pl.off_pc = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * 2 * kTile * 4);
   pl.off_m16 = off; off = align256(off + static_cast<size_t>(bh) * kMElems * 2);
   pl.off_sc = off; off = align256(off + static_cast<size_t>(bh) * kRedBlocks * 4);
-  pl.off_cmax = off; off = align256(off + static_cast<size_t>(bh) * pl.nchunks * kTile * 4);
   pl.off_cnt = off; off = align256(off + static_cast<size_t>(bh) * 2 * sizeof(uint32_t));  // fused kernel's counters
   pl.total = off;
   return pl;
@@ -1318,19 +1488,12 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   sp.ws.part_c = reinterpret_cast<float*>(w + pl.off_pc);
   sp.ws.m16 = reinterpret_cast<uint16_t*>(w + pl.off_m16);
   sp.ws.inv_scale = reinterpret_cast<float*>(w + pl.off_sc);
-  sp.ws.part_cmax = reinterpret_cast<float*>(w + pl.off_cmax);
   sp.ea = s.ea ? 1 : 0;
   sp.k = static_cast<const uint16_t*>(k_ptr);
   sp.k_sb = k_stride_b; sp.k_ss = k_stride_s; sp.k_sh = k_stride_h;
   sp.status = device_status_words();
 
   cudaError_t e;
-  if (s.ea) {
-    auto kern = s.bf16 ? ea_colmax_kernel<true> : ea_colmax_kernel<false>;
-    kern<<<static_cast<unsigned>(bh) * pl.nchunks, 256, 0, stream>>>(sp);
-    count_launch();
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  }
   {
     void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, StatsParams);
     if (s.ea) kern = s.bf16 ? sima_stats_kernel<true, true> : sima_stats_kernel<false, true>;
@@ -1373,7 +1536,7 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
       if (s.out_f32) kern = s.bf16 ? sima_out_kernel<true, true, false> : sima_out_kernel<false, true, false>;
       else kern = s.bf16 ? sima_out_kernel<true, false, false> : sima_out_kernel<false, false, false>;
     }
-    const uint32_t out_smem = s.ea ? kOutSmem - kTileBytes : kOutSmem;  // EA runs three Q stages
+    const uint32_t out_smem = out_smem_bytes(s.out_f32, s.ea);
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), static_cast<int>(out_smem));
     if (e != cudaSuccess) return e;
     kern<<<static_cast<unsigned>(bh) * op.nqchunks, kOutThreads + (s.ea ? 256 : 0), out_smem, stream>>>(mq, mm, s.out_f32 ? mq : mo, op);

@@ -348,6 +348,25 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
+// 2^x for a pair of values on the FMA pipe alone (no special-function unit): round to the nearest
+// integer with the 1.5 * 2^23 trick, a degree-4 polynomial on [-0.5, 0.5] (relative error below
+// 1e-6), the integer added into the exponent field.  x is clamped at -120 so that the result stays
+// a normal number; x must not exceed 127.
+__device__ __forceinline__ float2 ex2_fma_pipe2(float2 x) {
+  x.x = fmaxf(x.x, -120.f);
+  x.y = fmaxf(x.y, -120.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+  float2 p = make_float2(0.009570094756782055f, 0.009570094756782055f);
+  p = __ffma2_rn(p, f, make_float2(0.05591785907745361f, 0.05591785907745361f));
+  p = __ffma2_rn(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
+  p = __ffma2_rn(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+  p = __ffma2_rn(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
+}
+
 // ---------------------------------------------------------------------------------------------
 // 128-byte swizzle as TMA writes it: inside each 1024 B atom (8 rows of 128 B) the 16-byte chunk
 // index is XORed with (row mod 8).  `row` counts 128-byte rows from a 1024 B aligned base.
