@@ -146,6 +146,20 @@ __device__ __forceinline__ uint32_t max2_16(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t*>(&r);
   }
 }
+// true if either element of the packed pair a exceeds the matching element of b
+template <bool kBF16>
+__device__ __forceinline__ bool any_gt2_16(uint32_t a, uint32_t b) {
+  if constexpr (kBF16) {
+    const __nv_bfloat162 r = __hgt2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r) != 0u;
+  } else {
+    const __half2 r = __hgt2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r) != 0u;
+  }
+}
+// EA: how far (natural-log units) a value of K may exceed its column's reference before the
+// reference is raised; exp(8) = 2981 is far inside the range of both 16-bit types
+constexpr float kEaSlack = 8.0f;
 // EA: of the four pairs of exponentials per 16-byte chunk, how many go to the FMA pipe
 #ifndef ASUKA_EA_POLY_PAIRS
 #define ASUKA_EA_POLY_PAIRS 0
@@ -213,96 +227,11 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
 
-  // EA, pass A: the column maxima of this slab of K, which the exponentials of pass B are taken
-  // against (the reduce brings the slabs to a common reference).  K runs through the same stage
-  // ring, two tiles per stage (the V half holds the second one); its second read in pass B comes
-  // from L2.  `ring0` = ring positions used by pass A.
-  const int ring0 = kEA ? (ntile + 1) / 2 : 0;
-  if constexpr (kEA) {
-    if (warp == 0) {
-      if (lane == 0) {
-        const uint64_t keep = l2_policy_evict_last();  // pass B reads everything for the last time
-        for (int j = 0; j < ring0; ++j) {
-          const int st = j % kSt;
-          if (j >= kSt && !mbar_wait(smem_u32(&bars.empty[st]), (j / kSt - 1) & 1, abortp)) {
-            record_timeout(p.status, 46);
-            break;
-          }
-          const uint32_t bar = smem_u32(&bars.full[st]);
-          const uint32_t base = smem_base + st * kStageBytes;
-          const int nt = min(2, ntile - 2 * j);
-          mbar_expect_tx(bar, nt * kTileBytes);
-          for (int t = 0; t < nt; ++t) {
-            const int s0 = (tile0 + 2 * j + t) * kTile;
-            tma_load_4d_hint(base + t * kTileBytes, &map_k, bar, 0, h, s0, b, keep);
-            tma_load_4d_hint(base + t * kTileBytes + kHalfBytes, &map_k, bar, 64, h, s0, b, keep);
-          }
-        }
-      }
-    } else if (warp == 1) {
-      // no MMA in this pass: the warp stands in for the arrival its commit gives in pass B
-      for (int j = 0; j < ring0; ++j) {
-        const int st = j % kSt;
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (j / kSt) & 1, abortp))) {
-          if (lane == 0) record_timeout(p.status, 47);
-          break;
-        }
-        if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
-        __syncwarp();
-      }
-    } else if (warp >= 4) {
-      const int which = (warp - 4) >> 2;
-      const int t128 = tid - 128 - which * 128;
-      const int chunk16 = t128 & 15;
-      const int rg16 = which * 8 + (t128 >> 4);
-      uint32_t mxp[4];  // running maxima, packed as loaded (the maximum of 16-bit values is exact)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) mxp[e] = kBF16 ? 0xFF80FF80u : 0xFC00FC00u;  // -inf, -inf
-      for (int j = 0; j < ring0; ++j) {
-        const int st = j % kSt;
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (j / kSt) & 1, abortp))) {
-          if (lane == 0) record_timeout(p.status, 48);
-          break;
-        }
-        const int nt = min(2, ntile - 2 * j);
-        for (int t = 0; t < nt; ++t) {
-          const uint8_t* tile = smem_gen + st * kStageBytes + t * kTileBytes + (chunk16 >> 3) * kHalfBytes;
-          const int s0 = (tile0 + 2 * j + t) * kTile;
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const int row = rg16 + 16 * r;
-            const uint4 v = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
-            if (s0 + row < p.S) {  // (rows past the sequence were zero-filled by the load)
-              mxp[0] = max2_16<kBF16>(mxp[0], v.x);
-              mxp[1] = max2_16<kBF16>(mxp[1], v.y);
-              mxp[2] = max2_16<kBF16>(mxp[2], v.z);
-              mxp[3] = max2_16<kBF16>(mxp[3], v.w);
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
-      }
-      float mx[8];
-      unpack8<kBF16>(make_uint4(mxp[0], mxp[1], mxp[2], mxp[3]), mx);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) red[which][t128 >> 4][chunk16 * 8 + e] = mx[e];
-      named_bar_sync(1, 256);
-      if (which == 0) {
-        float m = -INFINITY;
-#pragma unroll
-        for (int g = 0; g < 8; ++g) m = fmaxf(m, fmaxf(red[0][g][t128], red[1][g][t128]));
-        cmax_s[t128] = m;
-      }
-      named_bar_sync(1, 256);  // cmax_s complete
-    }
-  }
-
   // stage layout: [K | V | Q] tiles
   if (warp == 0) {
     if (lane == 0) {
       for (int i = 0; i < ntile; ++i) {
-        const int k = ring0 + i;
+        const int k = i;
         const int st = k % kSt;
         if (k >= kSt && !mbar_wait(smem_u32(&bars.empty[st]), (k / kSt - 1) & 1, abortp)) {
           record_timeout(p.status, 41);
@@ -337,12 +266,11 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_MN_MAJOR, UMMA_MN_MAJOR, 128, 128);
       bool ok = true;
       for (int i = 0; i < ntile && ok; ++i) {
-        const int k = ring0 + i;
+        const int k = i;
         const int st = k % kSt;
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (k / kSt) & 1, abortp));
         if (!ok) { if (lane == 0) record_timeout(p.status, 42); break; }
         if constexpr (kEA) {
-          // (pass B is the only user of these barriers: its own step count picks one and gives the parity)
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.ktrans[i % kSt]), (i / kSt) & 1, abortp));
           if (!ok) { if (lane == 0) record_timeout(p.status, 45); break; }
         }
@@ -381,47 +309,132 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int chunk16 = t128 & 15;   // 8 consecutive channels
     const int rg = t128 >> 4;        // rows rg, rg+8, ...
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    const float kL2e = 1.4426950408889634f;
-    float2 ncm[4];  // EA: -(column maximum) * log2(e) of this thread's eight channels
-#pragma unroll
-    for (int e = 0; e < 4; ++e)
-      ncm[e] = kEA ? make_float2(-cmax_s[chunk16 * 8 + 2 * e] * kL2e, -cmax_s[chunk16 * 8 + 2 * e + 1] * kL2e)
-                   : make_float2(0.f, 0.f);
     bool ok = true;
-    for (int i = 0; i < ntile; ++i) {
-      const int k = ring0 + i;
-      const int st = k % kSt;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (k / kSt) & 1, abortp));
-      if (!ok) { if (lane == 0) record_timeout(p.status, 43); break; }
-      if constexpr (kEA) {
-        // all 256 threads work on the K tile: rows 16 apart per thread; k' = exp(k - colmax),
-        // rounded to the input type and written back for the MMA; rows past the sequence give 0
+    if constexpr (kEA) {
+      // All 256 threads work on the K tile, rows 16 apart per thread: k' = exp(k - ref), rounded to
+      // the input type and written back for the MMA; rows past the sequence give 0.  `ref` is a
+      // per-column reference for the whole slab (the reduce brings the slabs to a common one): the
+      // column maxima of the slab's first tile, raised -- with the accumulators scaled to match --
+      // whenever a later value exceeds it by more than kEaSlack, so that k' stays far inside the
+      // range of the 16-bit type.  On ordinary data the raise never happens after the first tile.
+      const int wq = warp & 3;
+      const int rg16 = which * 8 + rg;
+      const float kL2e = 1.4426950408889634f;
+      float2 nref[4] = {};   // -ref * log2(e) of this thread's eight channels
+      uint32_t thr[4] = {};  // ref + kEaSlack in the input type, packed
+      bool dead = false;     // a wait has given up: no more work, but every barrier is still taken
+      for (int i = 0; i < ntile; ++i) {
+        const int st = i % kSt;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kSt) & 1, abortp))) {
+          if (lane == 0 && !dead) record_timeout(p.status, 43);
+          dead = true;
+        }
         uint8_t* tile = smem_gen + st * kStageBytes + (chunk16 >> 3) * kHalfBytes;
-        const int rg16 = which * 8 + rg;
         const int s0 = (tile0 + i) * kTile;
+        uint4 raw[8];
+        uint32_t m4[4];  // maxima over this thread's rows, packed as loaded (exact for 16-bit values)
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          const int row = rg16 + 16 * r;
-          uint4* ptr = reinterpret_cast<uint4*>(tile + sw128_offset(row, chunk16 & 7));
-          if (s0 + row < p.S) {
-            const uint4 raw = *ptr;
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-            uint32_t o[4];
+        for (int e = 0; e < 4; ++e) m4[e] = kBF16 ? 0xFF80FF80u : 0xFC00FC00u;  // -inf, -inf
+        if (!dead) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 x = __ffma2_rn(unpack2_16<kBF16>(w[e]), make_float2(kL2e, kL2e), ncm[e]);
-              // half of the exponentials on the special-function unit, half on the FMA pipe
-              const float2 y = e < kEaPolyPairs ? ex2_fma_pipe2(x) : make_float2(ex2_approx(x.x), ex2_approx(x.y));
-              o[e] = pack2_16<kBF16>(y);
+          for (int r = 0; r < 8; ++r) {
+            const int row = rg16 + 16 * r;
+            raw[r] = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
+            if (s0 + row < p.S) {  // (rows past the sequence were zero-filled by the load)
+              m4[0] = max2_16<kBF16>(m4[0], raw[r].x);
+              m4[1] = max2_16<kBF16>(m4[1], raw[r].y);
+              m4[2] = max2_16<kBF16>(m4[2], raw[r].z);
+              m4[3] = max2_16<kBF16>(m4[3], raw[r].w);
             }
-            *ptr = make_uint4(o[0], o[1], o[2], o[3]);
-          } else {
-            *ptr = make_uint4(0u, 0u, 0u, 0u);
           }
         }
-        fence_proxy_async_smem();  // written by ordinary stores, read by the tensor pipe
-        mbar_arrive(smem_u32(&bars.ktrans[i % kSt]));
-      } else {
+        bool raise = i == 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) raise = raise || any_gt2_16<kBF16>(m4[e], thr[e]);
+        if (named_bar_or(1, 256, raise && !dead)) {
+          float mx[8];
+          unpack8<kBF16>(make_uint4(m4[0], m4[1], m4[2], m4[3]), mx);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) red[which][rg][chunk16 * 8 + e] = mx[e];
+          named_bar_sync(1, 256);
+          if (which == 0) {  // thread t128 = column d = TMEM lane d
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) tmax = fmaxf(tmax, fmaxf(red[0][g][t128], red[1][g][t128]));
+            const float old = cmax_s[t128];
+            const float nw = i == 0 ? tmax : fmaxf(old, tmax);
+            cmax_s[t128] = nw;
+            if (i > 0) {
+              // every MMA issued so far has retired once the release of the previous tile's stage
+              // has fired (the MMA of this tile waits for the arrivals below)
+              if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.empty[(i - 1) % kSt]), ((i - 1) / kSt) & 1, abortp))) {
+                if (lane == 0 && !dead) record_timeout(p.status, 46);
+                dead = true;
+              }
+              if (!dead) {
+                tc_fence_after_sync();
+                const float f = nw > old ? ex2_approx((old - nw) * kL2e) : 1.f;
+                const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  uint32_t u[32];
+                  tmem_ld32(tbase + lane_base + c * 32, u);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int x = 0; x < 32; ++x) u[x] = __float_as_uint(__uint_as_float(u[x]) * f);
+                  tmem_st32(tbase + lane_base + c * 32, u);
+                }
+                uint32_t u[16];
+                tmem_ld16(tbase + lane_base + 128, u);
+                tmem_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 16; ++x) u[x] = __float_as_uint(__uint_as_float(u[x]) * f);
+                tmem_st16(tbase + lane_base + 128, u);
+                tmem_wait_st();
+                tc_fence_before_sync();
+              }
+            }
+          }
+          named_bar_sync(1, 256);  // references updated, accumulators scaled
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float r0 = cmax_s[chunk16 * 8 + 2 * e], r1 = cmax_s[chunk16 * 8 + 2 * e + 1];
+            nref[e] = make_float2(-r0 * kL2e, -r1 * kL2e);
+            thr[e] = pack2_16<kBF16>(make_float2(r0 + kEaSlack, r1 + kEaSlack));
+          }
+          dead = dead || *abortp != 0u;
+        }
+        if (!dead) {
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int row = rg16 + 16 * r;
+            uint4* ptr = reinterpret_cast<uint4*>(tile + sw128_offset(row, chunk16 & 7));
+            if (s0 + row < p.S) {
+              const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
+              uint32_t o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 x = __ffma2_rn(unpack2_16<kBF16>(w[e]), make_float2(kL2e, kL2e), nref[e]);
+                const float2 y = e < kEaPolyPairs ? ex2_fma_pipe2(x) : make_float2(ex2_approx(x.x), ex2_approx(x.y));
+                o[e] = pack2_16<kBF16>(y);
+              }
+              *ptr = make_uint4(o[0], o[1], o[2], o[3]);
+            } else {
+              *ptr = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+          fence_proxy_async_smem();  // written by ordinary stores, read by the tensor pipe
+          mbar_arrive(smem_u32(&bars.ktrans[st]));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
+        }
+      }
+      ok = !dead;
+    } else {
+      for (int i = 0; i < ntile; ++i) {
+        const int st = i % kSt;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[st]), (i / kSt) & 1, abortp));
+        if (!ok) { if (lane == 0) record_timeout(p.status, 43); break; }
         const uint8_t* tile = smem_gen + st * kStageBytes + (which ? 2 * kTileBytes : 0) +
                               (chunk16 >> 3) * kHalfBytes;
 #pragma unroll
@@ -430,9 +443,9 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const uint4 v = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk16 & 7));
           abs_acc8<kBF16>(v, acc);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars.empty[st]));
     }
     if constexpr (kEA) {
       // slot 1 of the partial (SimA's sum|Q|): the slab's column maxima; slot 0 is written below

@@ -274,6 +274,28 @@ def test_ea_vs_oracle(ops, shape, dtype):
   no_timeouts(ops)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 4096, 2), (32, 2048, 8), (2, 1100, 1)])
+def test_ea_keys_that_grow_along_the_sequence(ops, shape, dtype):
+  # Every 128 keys the level of K steps up by more than the kernel lets a value exceed the running
+  # per-column reference of its slab of the sequence, so the reference is raised (and what has been
+  # accumulated is rescaled) again and again; one feature steps down instead, one is left alone.
+  B, S, H = shape
+  g = torch.Generator().manual_seed(7 * S + H)
+  q = torch.randn(B, S, H, 128, generator=g).to(dtype)
+  k = torch.randn(B, S, H, 128, generator=g)
+  v = torch.randn(B, S, H, 128, generator=g).to(dtype)
+  level = 10.0 * (torch.arange(S) // 128).to(torch.float32)
+  k = k + level[None, :, None, None]
+  k[..., 5] -= 2 * level[None, :, None]
+  k[..., 6] -= level[None, :, None]
+  k = k.to(dtype)
+  ref = O.ea(q, k, v)
+  close(ops.ea_fwd(q.cuda(), k.cuda(), v.cuda(), out_dtype=torch.float32), ref, "ea growing k, f32 out")
+  close(ops.ea_fwd(q.cuda(), k.cuda(), v.cuda()), ref, "ea growing k, 16-bit out")
+  no_timeouts(ops)
+
+
 @pytest.mark.parametrize("ea", [False, True])
 def test_linear_attention_blocks_at_the_reference_bench_shapes(ops, ea):
   # bench/sima.mlir / bench/ea.mlir: x [B, 784, 128] f32, 4 heads of 32; B reduced from 64 for the CPU oracle
