@@ -542,7 +542,7 @@ def main():
   if args.case in STREAMING:
     algo = io_bytes_of(args.case, ww, 1 if not main_mode["whole"] else w["B"])
     achieved = algo / (main_mode["resident"]["per_rank"][rank] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "ea_colmax + sima_stats + sima_reduce + sima_out (whole step)"
+    roofline = {"bound": "hbm", "kernel": "sima_stats + sima_reduce + sima_out in EA mode (whole step)"
                 if args.case == "ea" else "sima_fused_kernel (whole step: statistics, reduce and output in one launch)",
                 "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],

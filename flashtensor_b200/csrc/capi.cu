@@ -426,8 +426,7 @@ int sima_impl(const asuka_sima_params* p, void* ws, size_t ws_bytes, cudaStream_
   CUtensorMap m64[3];  // the same tensors in boxes of 64 rows, for the single-kernel path's first phase
   if ((r = make_map(&m64[0], p->q, 64)) || (r = make_map(&m64[1], p->k, 64)) || (r = make_map(&m64[2], p->v, 64))) return r;
   return map_cuda(launch_sima(mq, mk, mv, mo, p->out.ptr, p->out.stride[0], p->out.stride[1],
-                              p->out.stride[2], ws, sh, p->k.ptr, p->k.stride[0], p->k.stride[1],
-                              p->k.stride[2], m64, sms, stream));
+                              p->out.stride[2], ws, sh, m64, sms, stream));
 }
 
 // forward + column scores (+ selection) on one stream; the row statistic lives in `ws`

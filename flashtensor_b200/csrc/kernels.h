@@ -147,7 +147,6 @@ size_t sima_workspace_bytes(const SimaShape& s);
 cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                         const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
                         int64_t out_stride_s, int64_t out_stride_h, void* ws, const SimaShape& s,
-                        const void* k_ptr, int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
                         const CUtensorMap* maps64, int num_sms, cudaStream_t stream);  // maps64: q, k, v with 64-row boxes
 
 }  // namespace asuka

@@ -56,8 +56,6 @@ struct StatsParams {
   int B, H, S;
   int nchunks, tiles_per_chunk, ntiles;
   int ea;            // 1: the EA program (softmax normalisations), 0: SimA (L1 normalisations)
-  const uint16_t* k; // EA only: K [B,S,H,128] for the column-maximum pre-pass, strides in elements
-  int64_t k_sb, k_ss, k_sh;
   SimaWs ws;
   uint32_t* status;
 };
@@ -171,9 +169,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// kEA: the EA program.  K is exponentiated in place in shared memory against the column maxima
-// before the MMA reads it (so the product is exp(K - max)^T V and the column sums are the softmax
-// denominators); Q is not needed in this pass.
+// kEA: the EA program (softmax over the sequence of k, bench/ea.mlir:14).  K is exponentiated in
+// place in shared memory against a per-column reference of the slab before the MMA reads it, so
+// the product is exp(K - ref)^T V; the column sums of the same rounded values (a second, 16-column
+// MMA against a block of ones) are the slab's part of the softmax denominators.  The reduce brings
+// the slabs to a common reference.  Q is not needed in this pass.
 template <bool kBF16, bool kEA>
 __global__ void __launch_bounds__(kStThreads, 1)
 sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -185,7 +185,7 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) StBars bars;
   __shared__ float red[2][8][kTile];
-  __shared__ float cmax_s[kTile];
+  __shared__ float ref_s[kTile];
   // EA: a block of ones, the B operand of the small MMA that gives the column sums of the
   // exponentiated K (every element is 1, so its layout does not matter)
   __shared__ __align__(1024) uint16_t ones_s[kEA ? 1024 : 8];
@@ -361,9 +361,9 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             float tmax = -INFINITY;
 #pragma unroll
             for (int g = 0; g < 8; ++g) tmax = fmaxf(tmax, fmaxf(red[0][g][t128], red[1][g][t128]));
-            const float old = cmax_s[t128];
+            const float old = ref_s[t128];
             const float nw = i == 0 ? tmax : fmaxf(old, tmax);
-            cmax_s[t128] = nw;
+            ref_s[t128] = nw;
             if (i > 0) {
               // every MMA issued so far has retired once the release of the previous tile's stage
               // has fired (the MMA of this tile waits for the arrivals below)
@@ -398,7 +398,7 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           named_bar_sync(1, 256);  // references updated, accumulators scaled
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float r0 = cmax_s[chunk16 * 8 + 2 * e], r1 = cmax_s[chunk16 * 8 + 2 * e + 1];
+            const float r0 = ref_s[chunk16 * 8 + 2 * e], r1 = ref_s[chunk16 * 8 + 2 * e + 1];
             nref[e] = make_float2(-r0 * kL2e, -r1 * kL2e);
             thr[e] = pack2_16<kBF16>(make_float2(r0 + kEaSlack, r1 + kEaSlack));
           }
@@ -448,9 +448,9 @@ sima_stats_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
     }
     if constexpr (kEA) {
-      // slot 1 of the partial (SimA's sum|Q|): the slab's column maxima; slot 0 is written below
+      // slot 1 of the partial (SimA's sum|Q|): the slab's per-column reference; slot 0 is written below
       if (which == 1)
-        p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + 1) * kTile + t128] = cmax_s[t128];
+        p.ws.part_c[((static_cast<size_t>(bh) * p.nchunks + chunk) * 2 + 1) * kTile + t128] = ref_s[t128];
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) red[which][rg][chunk16 * 8 + i] = acc[i];
@@ -516,7 +516,7 @@ constexpr int kRedElems = kMElems / kRedBlocks;
 template <bool kBF16>
 __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p) {
   __shared__ float inv_c[kTile];
-  __shared__ float w_s[kMaxChunks][kTile];  // EA: exp(slab maximum - maximum), per slab and column
+  __shared__ float w_s[kMaxChunks][kTile];  // EA: exp(slab reference - largest reference), per slab and column
   __shared__ float wmax[8];
   __shared__ float s_scale;
   const int blk = blockIdx.x % kRedBlocks;
@@ -525,8 +525,8 @@ __global__ void __launch_bounds__(256, 4) sima_reduce_kernel(const StatsParams p
   const float* pm = p.ws.part_m + static_cast<size_t>(bh) * p.nchunks * kMElems + blk * kRedElems;
   if (tid < kTile) {
     if (p.ea) {
-      // each slab's exponentials were taken against the slab's own column maxima (slot 1): bring
-      // them to the maximum over the sequence.  A slab without rows has maximum -inf, weight 0.
+      // each slab's exponentials were taken against the slab's own per-column reference (slot 1):
+      // bring them to the largest of these
       float m = -INFINITY;
       for (int c = 0; c < p.nchunks; ++c) m = fmaxf(m, pc[(c * 2 + 1) * kTile + tid]);
       float ck = 0.f;
@@ -1447,7 +1447,6 @@ size_t sima_workspace_bytes(const SimaShape& s) { return make_plan(s).total; }
 cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                         const CUtensorMap& mo, void* out_ptr, int64_t out_stride_b,
                         int64_t out_stride_s, int64_t out_stride_h, void* ws, const SimaShape& s,
-                        const void* k_ptr, int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
                         const CUtensorMap* maps64, int num_sms, cudaStream_t stream) {
   const Plan pl = make_plan(s);
   const int bh = s.B * s.H;
@@ -1502,8 +1501,6 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   sp.ws.m16 = reinterpret_cast<uint16_t*>(w + pl.off_m16);
   sp.ws.inv_scale = reinterpret_cast<float*>(w + pl.off_sc);
   sp.ea = s.ea ? 1 : 0;
-  sp.k = static_cast<const uint16_t*>(k_ptr);
-  sp.k_sb = k_stride_b; sp.k_ss = k_stride_s; sp.k_sh = k_stride_h;
   sp.status = device_status_words();
 
   cudaError_t e;
