@@ -15,7 +15,9 @@ number too, as the secondary key `replicas`.
 
 Rank 0 prints ONE JSON line:
   value        algorithmic TFLOP/s of the whole job, inputs resident in HBM: median over `repeats`
-               timed loops of `steps` calls each (per loop: maximum over ranks)
+               timed loops of `steps` calls each (per loop: maximum over ranks); each call
+               replays the CUDA graph of the case's kernels for that input set (--no-graphs:
+               calls the case directly, which at small shapes measures the host)
   e2e          the same metric through the public per-case callable with HOST buffers: the timed
                region holds, for every step, the host->device copies of q, k, v from pinned memory
                and the device->host copies of every result; the package's host front end
@@ -373,6 +375,8 @@ def main():
                   help="a checkout of the reference: the CPU legs then time its own eager modules")
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--no-graphs", action="store_true",
+                  help="call the case directly for every timed step instead of replaying its CUDA graph")
   args = ap.parse_args()
   args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
   w = WORKLOADS[args.case]
@@ -430,12 +434,13 @@ def main():
       step(*sets[i % n_sets])
     barrier()
     mine, t_begin = [], time.time()
-    launches0 = ops.launch_count()
+    count = (lambda: step.launches) if hasattr(step, "launches") else ops.launch_count
+    launches0 = count()
     for _ in range(repeats):
       barrier()
       ms, _, _ = timed_loop(lambda i: step(*sets[i % n_sets]), args.steps)
       mine.append(ms / args.steps)
-    launches = (ops.launch_count() - launches0) // repeats
+    launches = (count() - launches0) // repeats
     t_end = time.time()
     barrier()
     rows = gather_rows(mine)                                     # [world][repeats]
@@ -469,7 +474,16 @@ def main():
       dist.all_reduce(t, op=dist.ReduceOp.MAX)
       repeats = int(t.item())
     res["repeats"] = repeats
-    res["resident"] = measure(step, sets, repeats)
+    resident_step = step
+    if not args.no_graphs:
+      # the kernels of a call, recorded once per input set and replayed: the host then spends one
+      # launch per call instead of descriptors, allocations and up to four launches
+      from flashtensor_b200.host import GraphedCall
+      resident_step = GraphedCall(step, max_graphs=n_sets)
+      for s_ in sets:
+        resident_step(*s_)
+      torch.cuda.synchronize()
+    res["resident"] = measure(resident_step, sets, repeats)
     if want_e2e:
       from flashtensor_b200.host import HostPipeline
       host_in = [t.cpu().pin_memory() for t in sets[0]]
@@ -549,9 +563,12 @@ def main():
                 "algorithmic_bytes_per_launch": algo}
   else:
     outs_k = [torch.empty_like(s[0]) for s in sets]
-    kern = lambda i: ops.attn_fwd(sets[i % n_sets][0], sets[i % n_sets][1], sets[i % n_sets][2],
-                                  causal=True, return_lse=True, out=outs_k[i % n_sets])
-    for i in range(3):
+    fwd = lambda q, k, v, o: ops.attn_fwd(q, k, v, causal=True, return_lse=True, out=o)
+    if not args.no_graphs:   # (a direct call costs the host more than this kernel takes at small shapes)
+      from flashtensor_b200.host import GraphedCall
+      fwd = GraphedCall(fwd, max_graphs=n_sets)
+    kern = lambda i: fwd(sets[i % n_sets][0], sets[i % n_sets][1], sets[i % n_sets][2], outs_k[i % n_sets])
+    for i in range(max(3, n_sets)):
       kern(i)
     barrier()
     reps, t_begin = [], time.time()
@@ -638,6 +655,8 @@ def main():
                     "ms_per_step_min": res["min"], "ms_per_step_max": res["max"],
                     "ms_times_sm_mhz": res["ms"] * sm if sm else None},
         "gpu_launches": res["launches"],
+        "launch_mode": ("direct calls of the case" if args.no_graphs else
+                        "CUDA graph of one call per input set, replayed (flashtensor_b200.host.GraphedCall)"),
         "roofline": roofline,
         "cpu_baseline": cpu,
         "clocks": {"sm_mhz": sm, "sm_max_mhz": clocks["sm_max_mhz"], "reasons": all_reasons,

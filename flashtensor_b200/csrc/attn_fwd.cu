@@ -49,6 +49,7 @@ struct FwdParams {
   int B, H, Sq, Skv;
   int causal, diag_off;
   int nq_blocks, n_items;
+  int pair_far, nq_tiles;    // pair_far: an item is the query tiles i and nq_tiles - 1 - i (see decode_item)
   int group;                 // query heads per key/value head (grouped-query attention)
   float scale_log2;          // softmax_scale * log2(e)
   float cap_in, cap_out;     // soft-capping: softmax_scale / cap and cap * log2(e)
@@ -154,12 +155,22 @@ template <bool kSplit>
 __device__ __forceinline__ void decode_item(int idx, const FwdParams& p, Item* item) {
   const int bh_count = p.B * p.H;
   if constexpr (!kSplit) {
-    const int qb = p.nq_blocks - 1 - idx / bh_count;
     const int bh = idx % bh_count;
     item->b = bh / p.H;
     item->h = bh % p.H;
-    item->q0[0] = qb * 2 * kTile;
-    item->q0[1] = qb * 2 * kTile + kTile;
+    if (p.pair_far) {
+      // A causal launch that fills at most one wave ends with its heaviest item, and items of
+      // adjacent tiles grow with the block index.  Pairing tile i with tile nq_tiles - 1 - i makes
+      // every item nq_tiles + 1 tile steps: the early tile shares the first key tiles with the
+      // late one, which then runs on alone.
+      const int i = idx / bh_count, far = p.nq_tiles - 1 - i;
+      item->q0[0] = i * kTile;
+      item->q0[1] = far > i ? far * kTile : p.Sq;  // (an odd count leaves the middle tile alone)
+    } else {
+      const int qb = p.nq_blocks - 1 - idx / bh_count;
+      item->q0[0] = qb * 2 * kTile;
+      item->q0[1] = qb * 2 * kTile + kTile;
+    }
     item->j0 = 0;
     item->n_kv[0] = kv_tiles_for(item->q0[0], p);
     item->n_kv[1] = kv_tiles_for(item->q0[1], p);
@@ -807,6 +818,12 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.nq_blocks = (s.Sq + 2 * kTile - 1) / (2 * kTile);
   p.parts = parts > 1 && split_ws != nullptr ? (parts < kMaxParts ? parts : kMaxParts) : 1;
   p.n_items = p.nq_blocks * s.B * s.H * p.parts;
+  p.nq_tiles = (s.Sq + kTile - 1) / kTile;
+#ifdef ASUKA_FWD_NO_PAIR_FAR
+  p.pair_far = 0;
+#else
+  p.pair_far = (p.parts == 1 && s.causal && p.n_items <= num_sms && p.nq_tiles >= 4) ? 1 : 0;
+#endif
   p.group = s.group;
   p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
   p.cap_in = s.softcap > 0.f ? s.softmax_scale / s.softcap : 0.f;
