@@ -1419,14 +1419,26 @@ struct Plan {
   size_t off_pm, off_pc, off_m16, off_sc, off_cnt, total;
 };
 
+// Into how many slabs the sequence of one (batch, head) unit is cut for the statistics and for the
+// output kernel of the three-kernel path: about seven waves of CTAs on a 148-SM part, but at least
+// eight tiles per CTA -- filling and draining the stage ring and loading M'' cost a CTA about as
+// much as four tiles -- unless that would leave SMs without a CTA.
+int slabs_per_unit(int bh, int ntiles) {
+  int want = (1024 + bh - 1) / bh;
+  const int long_enough = ntiles / 8 > 1 ? ntiles / 8 : 1;
+  if (want > long_enough) want = long_enough;
+  const int fill = (148 + bh - 1) / bh;
+  if (want < fill) want = fill;
+  if (want > ntiles) want = ntiles;
+  return want < 1 ? 1 : want;
+}
+
 Plan make_plan(const SimaShape& s) {
   Plan pl;
   const int bh = s.B * s.H;
   pl.ntiles = (s.S + kTile - 1) / kTile;
-  int want = (1024 + bh - 1) / bh;
-  if (want < 1) want = 1;
+  int want = slabs_per_unit(bh, pl.ntiles);
   if (want > kMaxChunks) want = kMaxChunks;
-  if (want > pl.ntiles) want = pl.ntiles;
   pl.tiles_per_chunk = (pl.ntiles + want - 1) / want;
   pl.nchunks = (pl.ntiles + pl.tiles_per_chunk - 1) / pl.tiles_per_chunk;
   size_t off = 0;
@@ -1528,10 +1540,7 @@ cudaError_t launch_sima(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     OutParams op;
     op.B = s.B; op.H = s.H; op.S = s.S;
     op.ntiles = pl.ntiles;
-    // enough CTAs for ~7 waves, at least 2 tiles each so that M'' is amortised
-    int nq = (1024 + bh - 1) / bh;
-    if (nq < 1) nq = 1;
-    if (nq > pl.ntiles) nq = pl.ntiles;
+    const int nq = slabs_per_unit(bh, pl.ntiles);
     op.tiles_per_cta = (pl.ntiles + nq - 1) / nq;
     op.nqchunks = (pl.ntiles + op.tiles_per_cta - 1) / op.tiles_per_cta;
     op.inv_scale = sp.ws.inv_scale;
