@@ -535,6 +535,285 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------------------------
+// Keyformer column pass with the noise operand staged by TMA.
+// The operand is read exactly once and is nine tenths of this pass's traffic; a thread that owns a
+// key (the transposed layout the MMA gives) would read its column of it with scalar loads, one
+// round trip to L2 or DRAM per 32 logits.  Here a CTA owns ONE key tile, which leaves shared
+// memory for a ring of noise pieces [64 queries x 128 keys] f32 (four 128-byte-swizzled boxes of
+// 32 keys, as in the row pass); two pieces are in flight while the third is consumed.  The sixteen
+// key warps are (TMEM lane quarter) x (16 of a piece's 64 queries).
+// ---------------------------------------------------------------------------------------------
+constexpr int kNzQStages = 2;
+constexpr int kNzStages = 3;
+constexpr int kNzRows = 64;                                  // queries per noise piece
+constexpr uint32_t kNzPieceBytes = kNzRows * kTile * 4;      // 32 KB
+constexpr uint32_t kNzBoxBytes = kNzPieceBytes / 4;          // one box: 32 keys x 64 queries
+constexpr uint32_t kNzSmemBytes = (1 + kNzQStages) * kTileBytes + kNzStages * kNzPieceBytes + 1024;
+
+struct NzBars {
+  uint64_t k_full;
+  uint64_t q_full[kNzQStages], q_empty[kNzQStages];
+  uint64_t s_full[2], s_empty[2];
+  uint64_t n_full[kNzStages], n_empty[kNzStages];
+};
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kThreads, 1)
+kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_n, const ColParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) NzBars bars;
+  __shared__ __align__(16) float lse_s[kNzQStages][kTile];  // minus the row statistic
+  __shared__ float part_s[4][kTile];                        // [which 16 queries][key]
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_s;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sK = smem_base;
+  const uint32_t sQ = smem_base + kTileBytes;
+  const uint32_t sN = sQ + kNzQStages * kTileBytes;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  volatile uint32_t* abortp = &abort_s;
+
+  const int bh_count = p.B * p.H;
+  const int blk = static_cast<int>(blockIdx.x) / bh_count;
+  const int kt = blk / p.n_qchunks;                    // low key tiles are the long ones
+  const int qc = p.n_qchunks - 1 - blk % p.n_qchunks;  // (late query ranges see the most keys)
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int b = bh / p.H, h = bh % p.H;
+  const int kv0 = kt * kTile;
+  const int i_lo = qc * p.q_chunk;
+  const int i_end = min(p.nq_tiles, i_lo + p.q_chunk);
+  // the first query tile of this CTA's range that can see the first key of the tile
+  const int i_begin = max(i_lo, p.causal ? max(0, kv0 - p.diag_off) / kTile : 0);
+  const int n_steps = max(0, i_end - i_begin);
+
+  if (!p.chained) griddep_wait();
+  griddep_launch_dependents();
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&bars.k_full), 1);
+    for (int i = 0; i < kNzQStages; ++i) {
+      mbar_init(smem_u32(&bars.q_full[i]), 1);
+      mbar_init(smem_u32(&bars.q_empty[i]), 1 + 16);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.s_full[i]), 1);
+      mbar_init(smem_u32(&bars.s_empty[i]), 512);
+    }
+    for (int i = 0; i < kNzStages; ++i) {
+      mbar_init(smem_u32(&bars.n_full[i]), 1);
+      mbar_init(smem_u32(&bars.n_empty[i]), 16);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_n);
+    const uint32_t bar = smem_u32(&bars.k_full);
+    mbar_expect_tx(bar, kTileBytes);
+    tma_load_4d(sK, &map_k, bar, 0, h / p.group, kv0, b);
+    tma_load_4d(sK + kHalfBytes, &map_k, bar, 64, h / p.group, kv0, b);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_s), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (whole warp)
+    // Order of issue: Q of step 0; then per step c its two noise pieces, then Q of step c + 1.
+    // A noise piece waits for the piece three before it to have been consumed, Q of step c + 1
+    // for step c - 1 to be over: while the key warps work on step c - 1 the two pieces of step c
+    // are in flight, and Q of step c + 1 arrives during step c.
+    const float* lse_row = p.lse2 + (static_cast<size_t>(b) * p.H + h) * p.Sq;
+    bool ok = true;
+    if (p.chained) griddep_wait();  // the row statistic is the output of the kernel ahead
+    auto load_q = [&](int c) -> bool {
+      const int i = i_begin + c;
+      const int st = c % kNzQStages;
+      const uint32_t use = static_cast<uint32_t>(c / kNzQStages);
+      if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_empty[st]), (use - 1) & 1, abortp))) {
+        if (lane == 0) record_timeout(p.status, 61);
+        return false;
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int qi = i * kTile + r * 32 + lane;
+        lse_s[st][r * 32 + lane] = qi < p.Sq ? -__ldg(lse_row + qi) : -INFINITY;
+      }
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t bar = smem_u32(&bars.q_full[st]);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sQ + st * kTileBytes, &map_q, bar, 0, h, i * kTile, b);
+        tma_load_4d(sQ + st * kTileBytes + kHalfBytes, &map_q, bar, 64, h, i * kTile, b);
+      }
+      return true;
+    };
+    uint32_t issued = 0;  // noise pieces issued
+    if (n_steps > 0) ok = load_q(0);
+    for (int c = 0; c < n_steps && ok; ++c) {
+      const int i = i_begin + c;
+      for (int pc = 0; pc < 2 && ok; ++pc, ++issued) {
+        const int ns = issued % kNzStages;
+        const uint32_t use = issued / kNzStages;
+        if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.n_empty[ns]), (use - 1) & 1, abortp))) {
+          if (lane == 0) record_timeout(p.status, 62);
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t bar = smem_u32(&bars.n_full[ns]);
+          mbar_expect_tx(bar, kNzPieceBytes);
+          for (int w = 0; w < 4; ++w)
+            tma_load_4d(sN + ns * kNzPieceBytes + w * kNzBoxBytes, &map_n, bar, kv0 + w * 32,
+                        i * kTile + pc * kNzRows, h, b);
+        }
+        __syncwarp();
+      }
+      if (ok && c + 1 < n_steps) ok = load_q(c + 1);
+    }
+    if (!ok && lane == 0) {
+      // give copies already in flight a bounded chance to land before the CTA retires
+      volatile uint32_t none = 0;
+      mbar_wait(smem_u32(&bars.k_full), 0, &none);
+      for (uint32_t x = issued > kNzStages ? issued - kNzStages : 0; x < issued; ++x)
+        mbar_wait(smem_u32(&bars.n_full[x % kNzStages]), (x / kNzStages) & 1, &none);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t kFmt = kBF16 ? UMMA_BF16 : UMMA_F16;
+    constexpr uint32_t idesc = umma_idesc_f16(kFmt, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t site) -> bool {
+      const bool good = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, abortp));
+      if (!good && lane == 0) record_timeout(p.status, site);
+      return good;
+    };
+    bool ok = wait_all(&bars.k_full, 0, 63);  // (also when there is no step: the copy must have landed)
+    const uint64_t kdesc = umma_smem_desc_sw128(sK, 16, 1024);
+    for (int c = 0; c < n_steps && ok; ++c) {
+      const int st = c % kNzQStages, buf = c & 1;
+      ok = wait_all(&bars.q_full[st], (c / kNzQStages) & 1, 64);
+      if (!ok) break;
+      if (c >= 2) {
+        ok = wait_all(&bars.s_empty[buf], ((c >> 1) - 1) & 1, 65);
+        if (!ok) break;
+      }
+      tc_fence_after_sync();
+      const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+          umma_ss(tbase + buf * 128, kdesc + off, qdesc + off, idesc, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars.s_full[buf]));
+        umma_commit(smem_u32(&bars.q_empty[st]));
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ one thread per (key, 16 of every 64 queries)
+    const int kw = warp - kUtilWarps;
+    const int sub = kw >> 2;   // which 16 queries of every piece
+    const int wq = warp & 3;   // TMEM lane quarter this warp may touch (four consecutive warps cover all four)
+    const int key = kv0 + wq * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float scale = p.scale_log2;
+    const float neg_inv_tau = -p.inv_tau;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    bool ok = true;
+    uint32_t nc = 0;  // noise pieces consumed
+    for (int c = 0; c < n_steps && ok; ++c) {
+      const int i = i_begin + c;
+      const int st = c % kNzQStages, buf = c & 1;
+      // S^T of this step is complete; its MMAs were issued after Q and the row statistics of the
+      // stage had landed, so this wait covers q_full as well
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[buf]), (c >> 1) & 1, abortp));
+      if (!ok) { if (lane == 0) record_timeout(p.status, 66); break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int pc = 0; pc < 2; ++pc, ++nc) {
+        const int ns = nc % kNzStages;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.n_full[ns]), (nc / kNzStages) & 1, abortp));
+        if (!ok) { if (lane == 0) record_timeout(p.status, 67); break; }
+        const int col0 = pc * kNzRows + sub * 16;  // first of this thread's 16 queries within the tile
+        uint32_t u[16];
+        tmem_ld16(tbase + lane_base + buf * 128 + col0, u);
+        // the thread's key is column `lane` of box wq; its queries are rows sub*16 .. +15
+        const uint8_t* box = smem_gen + (sN - smem_base) + ns * kNzPieceBytes + wq * kNzBoxBytes;
+        float nz[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int r = sub * 16 + e;
+          nz[e] = *reinterpret_cast<const float*>(box + sw128_offset(r, lane >> 2) + (lane & 3) * 4);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.n_empty[ns]));
+        tmem_wait_ld();
+        if (pc == 1) {
+          // this thread's part of the tile is in registers; when all 512 have said so the MMA
+          // warp may overwrite the TMEM buffer
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&bars.s_empty[buf]));
+        }
+        const int q_base = i * kTile + col0;
+        // query q sees `key` iff key <= q + diag_off
+        const int first_visible = p.causal ? key - p.diag_off - q_base : 0;
+        const float4* lse4 = reinterpret_cast<const float4*>(lse_s[st]) + (col0 >> 2);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const float4 L = lse4[g];
+          const float lv[4] = {L.x, L.y, L.z, L.w};  // minus the row statistic (-inf past the last query)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int cc = g * 4 + e;
+            // (rows and keys past the tensor's end are zero-filled by the copy: keep lg2 finite,
+            // the row statistic of -inf or the bounds check at the end removes them)
+            const float l2 = lg2(fmaxf(nz[cc], 1e-30f));
+            const float x = fmaf(__uint_as_float(u[cc]), scale, fmaf(l2, neg_inv_tau, lv[e]));
+            const float pr = cc < first_visible ? 0.f : ex2(x);
+            acc[e] += pr;
+          }
+        }
+      }
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars.q_empty[st]));
+    }
+    part_s[sub][wq * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    if (!ok) *abortp = 1u;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, 256);
+  }
+  if (warp >= kUtilWarps && ((warp - kUtilWarps) >> 2) == 0 && !*abortp) {
+    const int k_in_tile = (warp & 3) * 32 + lane;
+    const int key = kv0 + k_in_tile;
+    if (key < p.Skv) {
+      const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
+      const float v = (part_s[0][k_in_tile] + part_s[1][k_in_tile]) + (part_s[2][k_in_tile] + part_s[3][k_in_tile]);
+      const size_t slab = static_cast<size_t>(qc) * bh_count * p.Skv;
+      (p.n_qchunks > 1 ? p.part + slab : p.score)[o] = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Keyformer row pass: lse2'[row] = log2 sum_j exp2(((s_ij*scale + g_ij)/tau) * log2e)
 // One CTA per 128 query rows; one thread per row; K tiles stream through a ring.
 // kNoiseTma: the [128 x 128] f32 noise tile of every step is staged in shared memory by TMA
@@ -868,6 +1147,30 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
     p.part = static_cast<float*>(split_ws);
     p.part_sq = p.part + static_cast<size_t>(p.n_qchunks) * s.B * s.H * s.Skv;
   }
+  cudaError_t e;
+#ifndef ASUKA_COL_NO_NOISE_TMA
+  // Keyformer with a noise operand that TMA can describe (16-byte aligned base, strides that are
+  // multiples of 16 bytes): the variant that stages the operand in shared memory
+  if (a.mode == ASUKA_SCORE_PERTURBED && a.exp_rand != nullptr &&
+      (reinterpret_cast<uintptr_t>(a.exp_rand) & 15u) == 0 && a.er_stride_q % 4 == 0 && a.er_stride_h % 4 == 0 &&
+      a.er_stride_b % 4 == 0 && a.er_stride_q > 0 && a.er_stride_h > 0 && a.er_stride_b > 0) {
+    CUtensorMap mn;
+    const uint64_t dims[4] = {static_cast<uint64_t>(s.Skv), static_cast<uint64_t>(s.Sq),
+                              static_cast<uint64_t>(s.H), static_cast<uint64_t>(s.B)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(a.er_stride_q) * 4, static_cast<uint64_t>(a.er_stride_h) * 4,
+                                 static_cast<uint64_t>(a.er_stride_b) * 4};
+    const uint32_t box[4] = {32, kNzRows, 1, 1};
+    if (tma_host::make_f32_map_sw128(&mn, a.exp_rand, dims, strides, box) != 0) return cudaErrorInvalidValue;
+    auto nk = s.bf16 ? kf_col_tma_kernel<true> : kf_col_tma_kernel<false>;
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(nk), kNzSmemBytes);
+    if (e != cudaSuccess) return e;
+    const int n_kt = (s.Skv + kTile - 1) / kTile;
+    e = launch_dependent(nk, dim3(static_cast<unsigned>(n_kt) * p.n_qchunks * s.B * s.H), dim3(kThreads), kNzSmemBytes,
+                         stream, mq, mk, mn, p);
+    count_launch();
+  } else
+#endif
+  {
   const int n_kvb = (s.Skv + 2 * kTile - 1) / (2 * kTile);
   const dim3 grid(static_cast<unsigned>(n_kvb) * p.n_qchunks * s.B * s.H);
   void (*kern)(CUtensorMap, CUtensorMap, ColParams) = nullptr;
@@ -876,10 +1179,11 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
   else if (a.mode == ASUKA_SCORE_CORM) kern = s.bf16 ? col_scores_kernel<true, 4> : col_scores_kernel<false, 4>;
   else if (a.exp_rand != nullptr) kern = s.bf16 ? col_scores_kernel<true, 2> : col_scores_kernel<false, 2>;
   else kern = s.bf16 ? col_scores_kernel<true, 3> : col_scores_kernel<false, 3>;
-  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
+  e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (e != cudaSuccess) return e;
   e = launch_dependent(kern, grid, dim3(kThreads), kSmemBytes, stream, mq, mk, p);
   count_launch();
+  }
   if (e != cudaSuccess || p.n_qchunks == 1) return e;
   const size_t n = static_cast<size_t>(s.B) * s.H * s.Skv;
   const bool sq = a.mode == ASUKA_SCORE_SUM_SQ;
