@@ -50,6 +50,7 @@ struct FwdParams {
   int causal, diag_off;
   int nq_blocks, n_items;
   int pair_far, nq_tiles;    // pair_far: an item is the query tiles i and nq_tiles - 1 - i (see decode_item)
+  int unit_major;            // items are numbered unit by unit instead of heaviest block first
   int group;                 // query heads per key/value head (grouped-query attention)
   float scale_log2;          // softmax_scale * log2(e)
   float cap_in, cap_out;     // soft-capping: softmax_scale / cap and cap * log2(e)
@@ -155,10 +156,18 @@ template <bool kSplit>
 __device__ __forceinline__ void decode_item(int idx, const FwdParams& p, Item* item) {
   const int bh_count = p.B * p.H;
   if constexpr (!kSplit) {
-    const int bh = idx % bh_count;
+    // unit_major: the blocks of one (batch, head) follow each other, latest first, so that they
+    // run at about the same time and K/V are in L2 for all but the first of them.  It is used
+    // when K and V of the whole launch do not fit L2 (otherwise every wave of blocks would fetch
+    // them from DRAM again).
+    const int bh = p.unit_major ? idx / p.nq_blocks : idx % bh_count;
     item->b = bh / p.H;
     item->h = bh % p.H;
-    if (p.pair_far) {
+    if (p.unit_major) {
+      const int qb = p.nq_blocks - 1 - idx % p.nq_blocks;
+      item->q0[0] = qb * 2 * kTile;
+      item->q0[1] = qb * 2 * kTile + kTile;
+    } else if (p.pair_far) {
       // A causal launch that fills at most one wave ends with its heaviest item, and items of
       // adjacent tiles grow with the block index.  Pairing tile i with tile nq_tiles - 1 - i makes
       // every item nq_tiles + 1 tile steps: the early tile shares the first key tiles with the
@@ -819,6 +828,14 @@ cudaError_t launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const 
   p.parts = parts > 1 && split_ws != nullptr ? (parts < kMaxParts ? parts : kMaxParts) : 1;
   p.n_items = p.nq_blocks * s.B * s.H * p.parts;
   p.nq_tiles = (s.Sq + kTile - 1) / kTile;
+  {
+    const double kv_bytes = 2.0 * s.B * (s.H / (s.group > 0 ? s.group : 1)) * static_cast<double>(s.Skv) * 128 * 2;
+#ifdef ASUKA_FWD_NO_UNIT_MAJOR
+    p.unit_major = 0;
+#else
+    p.unit_major = (p.parts == 1 && p.n_items > num_sms && kv_bytes > 96e6) ? 1 : 0;
+#endif
+  }
 #ifdef ASUKA_FWD_NO_PAIR_FAR
   p.pair_far = 0;
 #else
