@@ -873,8 +873,12 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   // (longest) first, so that K, which every one of them reads, comes from DRAM once -- with two
   // gigabytes of noise streaming through L2 it does not survive from one wave to a later one
   // (measured before the change: 1.65 GB read where 1.27 GB were needed).
-  const int bh = static_cast<int>(blockIdx.x) / p.nq_tiles;
-  const int qt = p.nq_tiles - 1 - static_cast<int>(blockIdx.x) % p.nq_tiles;
+  // The seeded variant reads no operand and is bound by its generator: it keeps the order
+  // longest tile first over all units, which balances the SMs better.
+  constexpr bool kUnitMajor = kNoise != 2;
+  const int bh = kUnitMajor ? static_cast<int>(blockIdx.x) / p.nq_tiles : static_cast<int>(blockIdx.x) % bh_count;
+  const int qt = p.nq_tiles - 1 - (kUnitMajor ? static_cast<int>(blockIdx.x) % p.nq_tiles
+                                              : static_cast<int>(blockIdx.x) / bh_count);
   const int b = bh / p.H, h = bh % p.H;
   const int q0 = qt * kTile;
   int last = p.Skv - 1;
