@@ -190,6 +190,23 @@ def test_keyformer_vs_oracle(ops, shape, dtype):
   no_timeouts(ops)
 
 
+@pytest.mark.parametrize("skv", [4100, 4101])
+def test_keyformer_long_sequence_with_few_heads_vs_oracle(ops, skv):
+  # two heads of a long sequence: the forward kernel splits key ranges, the column pass splits
+  # query ranges (partial sums per range, added in range order).  A row length of 4100 floats is
+  # one TMA can describe (the passes stage the noise operand in shared memory), 4101 is not (they
+  # read it with plain loads).
+  B, H, Sq = 1, 2, 4100
+  q, k, v, er = O.make_inputs("keyformer", B, Sq, skv, H, 128, torch.float16, seed=skv)
+  ref_out, ref_score = O.keyformer(q, k, v, er, tau=1.5)
+  out, score = ops.keyformer(q.cuda(), k.cuda(), v.cuda(), er.cuda(), tau=1.5)
+  torch.cuda.synchronize()
+  close(out, ref_out, "out")
+  close(score, ref_score, "kf_score")
+  torch.testing.assert_close(score.sum(-1).cpu(), torch.full((B, H), float(Sq)), rtol=1e-4, atol=1e-3)
+  no_timeouts(ops)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 256, 256, 2), (2, 640, 640, 3), (1, 100, 333, 2)])
 def test_keyformer_seeded_noise_vs_oracle(ops, shape, dtype):
