@@ -541,7 +541,8 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // round trip to L2 or DRAM per 32 logits.  Here a CTA owns ONE key tile, which leaves shared
 // memory for a ring of noise pieces [64 queries x 128 keys] f32 (four 128-byte-swizzled boxes of
 // 32 keys, as in the row pass); two pieces are in flight while the third is consumed.  The sixteen
-// key warps are (TMEM lane quarter) x (16 of a piece's 64 queries).
+// key warps are (TMEM lane quarter) x (16 of a piece's 64 queries).  A CTA takes two key tiles in
+// turn (see the comment on segments in the kernel).
 // ---------------------------------------------------------------------------------------------
 constexpr int kNzQStages = 2;
 constexpr int kNzStages = 3;
@@ -564,7 +565,7 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) NzBars bars;
   __shared__ __align__(16) float lse_s[kNzQStages][kTile];  // minus the row statistic
-  __shared__ float part_s[4][kTile];                        // [which 16 queries][key]
+  __shared__ float part_s[2][4][kTile];                     // [segment][which 16 queries][key]
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
 
@@ -582,19 +583,29 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   // Unit-major grid: the key tiles of one (batch, head) run at about the same time, so that Q,
   // which every one of them reads, comes from DRAM once (the noise streaming through L2 would
   // have pushed it out by the time a later wave asked for it again).
+  // A CTA works through TWO key tiles, one after the other ("segments"): tile i and tile
+  // n - 1 - i, which under a causal mask together always make n + 1 steps, so all CTAs are equally
+  // long and there are half as many set-ups and drains.  The Q, noise and TMEM rings run on
+  // across the change of segment; only K is reloaded, while the key warps still work on the
+  // first segment's last step.
   const int bh_count = p.B * p.H;
-  const int per_unit = static_cast<int>(gridDim.x) / bh_count;  // key tiles x query ranges
+  const int n_kt = (p.Skv + kTile - 1) / kTile;
+  const int per_unit = static_cast<int>(gridDim.x) / bh_count;  // pairs of key tiles x query ranges
   const int blk = static_cast<int>(blockIdx.x) % per_unit;
-  const int kt = blk / p.n_qchunks;                    // low key tiles are the long ones
+  const int pair = blk / p.n_qchunks;
   const int qc = p.n_qchunks - 1 - blk % p.n_qchunks;  // (late query ranges see the most keys)
   const int bh = static_cast<int>(blockIdx.x) / per_unit;
   const int b = bh / p.H, h = bh % p.H;
-  const int kv0 = kt * kTile;
+  const int kts[2] = {pair, n_kt - 1 - pair};
+  const int n_seg = kts[1] > kts[0] ? 2 : 1;  // (an odd count leaves the middle tile alone)
   const int i_lo = qc * p.q_chunk;
   const int i_end = min(p.nq_tiles, i_lo + p.q_chunk);
-  // the first query tile of this CTA's range that can see the first key of the tile
-  const int i_begin = max(i_lo, p.causal ? max(0, kv0 - p.diag_off) / kTile : 0);
-  const int n_steps = max(0, i_end - i_begin);
+  // first key, first query tile of this CTA's range that can see it, and number of steps of segment s
+  auto segment = [&](int sgm, int& kv0, int& i_begin, int& n_steps) {
+    kv0 = kts[sgm] * kTile;
+    i_begin = max(i_lo, p.causal ? max(0, kv0 - p.diag_off) / kTile : 0);
+    n_steps = max(0, i_end - i_begin);
+  };
 
   if (!p.chained) griddep_wait();
   griddep_launch_dependents();
@@ -618,10 +629,6 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_n);
-    const uint32_t bar = smem_u32(&bars.k_full);
-    mbar_expect_tx(bar, kTileBytes);
-    tma_load_4d(sK, &map_k, bar, 0, h / p.group, kv0, b);
-    tma_load_4d(sK + kHalfBytes, &map_k, bar, 64, h / p.group, kv0, b);
   }
   if (warp == 1) {
     __syncwarp();
@@ -633,19 +640,20 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
 
+  // Steps and noise pieces are counted through both segments: ring stages and barrier parities
+  // follow from the running counts.
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (whole warp)
-    // Order of issue: Q of step 0; then per step c its two noise pieces, then Q of step c + 1.
-    // A noise piece waits for the piece three before it to have been consumed, Q of step c + 1
-    // for step c - 1 to be over: while the key warps work on step c - 1 the two pieces of step c
-    // are in flight, and Q of step c + 1 arrives during step c.
+    // Order of issue within a segment: K; Q of its first step; then per step its two noise
+    // pieces, then Q of the next step.  A noise piece waits for the piece three before it to have
+    // been consumed, Q of step c + 1 for step c - 1 to be over: while the key warps work on step
+    // c - 1 the two pieces of step c are in flight, and Q of step c + 1 arrives during step c.
     const float* lse_row = p.lse2 + (static_cast<size_t>(b) * p.H + h) * p.Sq;
     bool ok = true;
     if (p.chained) griddep_wait();  // the row statistic is the output of the kernel ahead
-    auto load_q = [&](int c) -> bool {
-      const int i = i_begin + c;
-      const int st = c % kNzQStages;
-      const uint32_t use = static_cast<uint32_t>(c / kNzQStages);
+    auto load_q = [&](uint32_t cg, int i) -> bool {  // cg: running step count, i: query tile
+      const int st = cg % kNzQStages;
+      const uint32_t use = cg / kNzQStages;
       if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.q_empty[st]), (use - 1) & 1, abortp))) {
         if (lane == 0) record_timeout(p.status, 61);
         return false;
@@ -664,42 +672,67 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       return true;
     };
-    uint32_t issued = 0;  // noise pieces issued
+    uint32_t issued = 0;   // noise pieces issued
+    uint32_t cg0 = 0;      // steps of the segments before this one
+    uint32_t k_loads = 0;
     const uint64_t stream_once = l2_policy_evict_first();
-    if (n_steps > 0) ok = load_q(0);
-    for (int c = 0; c < n_steps && ok; ++c) {
-      const int i = i_begin + c;
-      for (int pc = 0; pc < 2 && ok; ++pc, ++issued) {
-        const int ns = issued % kNzStages;
-        const uint32_t use = issued / kNzStages;
-        if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.n_empty[ns]), (use - 1) & 1, abortp))) {
-          if (lane == 0) record_timeout(p.status, 62);
+    for (int sgm = 0; sgm < n_seg && ok; ++sgm) {
+      int kv0, i_begin, n_steps;
+      segment(sgm, kv0, i_begin, n_steps);
+      if (n_steps == 0) continue;
+      if (cg0 > 0) {
+        // the K buffer is free once the last MMA that read it has retired
+        const uint32_t last = cg0 - 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[last & 1]), (last >> 1) & 1, abortp))) {
+          if (lane == 0) record_timeout(p.status, 68);
           ok = false;
           break;
         }
-        if (lane == 0) {
-          const uint32_t bar = smem_u32(&bars.n_full[ns]);
-          // boxes whose first key no query of the piece can see are not fetched (their threads
-          // mask every value of the piece); the operand is read once: first to leave L2
-          const int q_last = i * kTile + pc * kNzRows + kNzRows - 1;
-          int n_vis = 4;
-          if (p.causal) {
-            const int d = q_last + p.diag_off - kv0;  // last visible key of the piece, relative to the tile
-            n_vis = d < 0 ? 0 : min(4, d / 32 + 1);
-          }
-          mbar_expect_tx(bar, n_vis * kNzBoxBytes);
-          for (int w = 0; w < n_vis; ++w)
-            tma_load_4d_hint(sN + ns * kNzPieceBytes + w * kNzBoxBytes, &map_n, bar, kv0 + w * 32,
-                             i * kTile + pc * kNzRows, h, b, stream_once);
-        }
-        __syncwarp();
       }
-      if (ok && c + 1 < n_steps) ok = load_q(c + 1);
+      if (lane == 0) {
+        const uint32_t bar = smem_u32(&bars.k_full);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(sK, &map_k, bar, 0, h / p.group, kv0, b);
+        tma_load_4d(sK + kHalfBytes, &map_k, bar, 64, h / p.group, kv0, b);
+      }
+      ++k_loads;
+      __syncwarp();
+      ok = load_q(cg0, i_begin);
+      for (int c = 0; c < n_steps && ok; ++c) {
+        const int i = i_begin + c;
+        for (int pc = 0; pc < 2 && ok; ++pc, ++issued) {
+          const int ns = issued % kNzStages;
+          const uint32_t use = issued / kNzStages;
+          if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.n_empty[ns]), (use - 1) & 1, abortp))) {
+            if (lane == 0) record_timeout(p.status, 62);
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            const uint32_t bar = smem_u32(&bars.n_full[ns]);
+            // boxes whose first key no query of the piece can see are not fetched (their threads
+            // mask every value of the piece); the operand is read once: first to leave L2
+            const int q_last = i * kTile + pc * kNzRows + kNzRows - 1;
+            int n_vis = 4;
+            if (p.causal) {
+              const int d = q_last + p.diag_off - kv0;  // last visible key of the piece, relative to the tile
+              n_vis = d < 0 ? 0 : min(4, d / 32 + 1);
+            }
+            mbar_expect_tx(bar, n_vis * kNzBoxBytes);
+            for (int w = 0; w < n_vis; ++w)
+              tma_load_4d_hint(sN + ns * kNzPieceBytes + w * kNzBoxBytes, &map_n, bar, kv0 + w * 32,
+                               i * kTile + pc * kNzRows, h, b, stream_once);
+          }
+          __syncwarp();
+        }
+        if (ok && c + 1 < n_steps) ok = load_q(cg0 + c + 1, i + 1);
+      }
+      cg0 += static_cast<uint32_t>(n_steps);
     }
     if (!ok && lane == 0) {
       // give copies already in flight a bounded chance to land before the CTA retires
       volatile uint32_t none = 0;
-      mbar_wait(smem_u32(&bars.k_full), 0, &none);
+      if (k_loads > 0) mbar_wait(smem_u32(&bars.k_full), (k_loads - 1) & 1, &none);
       for (uint32_t x = issued > kNzStages ? issued - kNzStages : 0; x < issued; ++x)
         mbar_wait(smem_u32(&bars.n_full[x % kNzStages]), (x / kNzStages) & 1, &none);
     }
@@ -712,99 +745,116 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (!good && lane == 0) record_timeout(p.status, site);
       return good;
     };
-    bool ok = wait_all(&bars.k_full, 0, 63);  // (also when there is no step: the copy must have landed)
+    bool ok = true;
+    uint32_t cg0 = 0, k_loads = 0;
     const uint64_t kdesc = umma_smem_desc_sw128(sK, 16, 1024);
-    for (int c = 0; c < n_steps && ok; ++c) {
-      const int st = c % kNzQStages, buf = c & 1;
-      ok = wait_all(&bars.q_full[st], (c / kNzQStages) & 1, 64);
-      if (!ok) break;
-      if (c >= 2) {
-        ok = wait_all(&bars.s_empty[buf], ((c >> 1) - 1) & 1, 65);
+    for (int sgm = 0; sgm < n_seg && ok; ++sgm) {
+      int kv0, i_begin, n_steps;
+      segment(sgm, kv0, i_begin, n_steps);
+      if (n_steps == 0) continue;
+      ok = wait_all(&bars.k_full, k_loads & 1, 63);
+      ++k_loads;
+      for (int c = 0; c < n_steps && ok; ++c) {
+        const uint32_t cg = cg0 + c;
+        const int st = cg % kNzQStages, buf = cg & 1;
+        ok = wait_all(&bars.q_full[st], (cg / kNzQStages) & 1, 64);
         if (!ok) break;
-      }
-      tc_fence_after_sync();
-      const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
-          umma_ss(tbase + buf * 128, kdesc + off, qdesc + off, idesc, kk > 0 ? 1u : 0u);
+        if (cg >= 2) {
+          ok = wait_all(&bars.s_empty[buf], ((cg >> 1) - 1) & 1, 65);
+          if (!ok) break;
         }
-        umma_commit(smem_u32(&bars.s_full[buf]));
-        umma_commit(smem_u32(&bars.q_empty[st]));
+        tc_fence_after_sync();
+        const uint64_t qdesc = umma_smem_desc_sw128(sQ + st * kTileBytes, 16, 1024);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = static_cast<uint64_t>((kk & 3) * 2 + (kk >> 2) * (kHalfBytes >> 4));
+            umma_ss(tbase + buf * 128, kdesc + off, qdesc + off, idesc, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars.s_full[buf]));
+          umma_commit(smem_u32(&bars.q_empty[st]));
+        }
+        __syncwarp();
       }
-      __syncwarp();
+      cg0 += static_cast<uint32_t>(n_steps);
     }
   } else {
     // ------------------------------------------------------------------ one thread per (key, 16 of every 64 queries)
     const int kw = warp - kUtilWarps;
     const int sub = kw >> 2;   // which 16 queries of every piece
     const int wq = warp & 3;   // TMEM lane quarter this warp may touch (four consecutive warps cover all four)
-    const int key = kv0 + wq * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float scale = p.scale_log2;
     const float neg_inv_tau = -p.inv_tau;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     bool ok = true;
-    uint32_t nc = 0;  // noise pieces consumed
-    for (int c = 0; c < n_steps && ok; ++c) {
-      const int i = i_begin + c;
-      const int st = c % kNzQStages, buf = c & 1;
-      // S^T of this step is complete; its MMAs were issued after Q and the row statistics of the
-      // stage had landed, so this wait covers q_full as well
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[buf]), (c >> 1) & 1, abortp));
-      if (!ok) { if (lane == 0) record_timeout(p.status, 66); break; }
-      tc_fence_after_sync();
+    uint32_t nc = 0;   // noise pieces consumed
+    uint32_t cg0 = 0;  // steps of the segments before this one
+    for (int sgm = 0; sgm < n_seg; ++sgm) {
+      int kv0, i_begin, n_steps;
+      segment(sgm, kv0, i_begin, n_steps);
+      const int key = kv0 + wq * 32 + lane;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = 0; c < n_steps && ok; ++c) {
+        const int i = i_begin + c;
+        const uint32_t cg = cg0 + c;
+        const int st = cg % kNzQStages, buf = cg & 1;
+        // S^T of this step is complete; its MMAs were issued after Q and the row statistics of the
+        // stage had landed, so this wait covers q_full as well
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[buf]), (cg >> 1) & 1, abortp));
+        if (!ok) { if (lane == 0) record_timeout(p.status, 66); break; }
+        tc_fence_after_sync();
 #pragma unroll
-      for (int pc = 0; pc < 2; ++pc, ++nc) {
-        const int ns = nc % kNzStages;
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.n_full[ns]), (nc / kNzStages) & 1, abortp));
-        if (!ok) { if (lane == 0) record_timeout(p.status, 67); break; }
-        const int col0 = pc * kNzRows + sub * 16;  // first of this thread's 16 queries within the tile
-        uint32_t u[16];
-        tmem_ld16(tbase + lane_base + buf * 128 + col0, u);
-        // the thread's key is column `lane` of box wq; its queries are rows sub*16 .. +15
-        const uint8_t* box = smem_gen + (sN - smem_base) + ns * kNzPieceBytes + wq * kNzBoxBytes;
-        float nz[16];
+        for (int pc = 0; pc < 2; ++pc, ++nc) {
+          const int ns = nc % kNzStages;
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.n_full[ns]), (nc / kNzStages) & 1, abortp));
+          if (!ok) { if (lane == 0) record_timeout(p.status, 67); break; }
+          const int col0 = pc * kNzRows + sub * 16;  // first of this thread's 16 queries within the tile
+          uint32_t u[16];
+          tmem_ld16(tbase + lane_base + buf * 128 + col0, u);
+          // the thread's key is column `lane` of box wq; its queries are rows sub*16 .. +15
+          const uint8_t* box = smem_gen + (sN - smem_base) + ns * kNzPieceBytes + wq * kNzBoxBytes;
+          float nz[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int r = sub * 16 + e;
-          nz[e] = *reinterpret_cast<const float*>(box + sw128_offset(r, lane >> 2) + (lane & 3) * 4);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars.n_empty[ns]));
-        tmem_wait_ld();
-        if (pc == 1) {
-          // this thread's part of the tile is in registers; when all 512 have said so the MMA
-          // warp may overwrite the TMEM buffer
-          tc_fence_before_sync();
-          mbar_arrive(smem_u32(&bars.s_empty[buf]));
-        }
-        const int q_base = i * kTile + col0;
-        // query q sees `key` iff key <= q + diag_off
-        const int first_visible = p.causal ? key - p.diag_off - q_base : 0;
-        const float4* lse4 = reinterpret_cast<const float4*>(lse_s[st]) + (col0 >> 2);
+          for (int e = 0; e < 16; ++e) {
+            const int r = sub * 16 + e;
+            nz[e] = *reinterpret_cast<const float*>(box + sw128_offset(r, lane >> 2) + (lane & 3) * 4);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars.n_empty[ns]));
+          tmem_wait_ld();
+          if (pc == 1) {
+            // this thread's part of the tile is in registers; when all 512 have said so the MMA
+            // warp may overwrite the TMEM buffer
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars.s_empty[buf]));
+          }
+          const int q_base = i * kTile + col0;
+          // query q sees `key` iff key <= q + diag_off
+          const int first_visible = p.causal ? key - p.diag_off - q_base : 0;
+          const float4* lse4 = reinterpret_cast<const float4*>(lse_s[st]) + (col0 >> 2);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const float4 L = lse4[g];
-          const float lv[4] = {L.x, L.y, L.z, L.w};  // minus the row statistic (-inf past the last query)
+          for (int g = 0; g < 4; ++g) {
+            const float4 L = lse4[g];
+            const float lv[4] = {L.x, L.y, L.z, L.w};  // minus the row statistic (-inf past the last query)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int cc = g * 4 + e;
-            // (rows and keys past the tensor's end are zero-filled by the copy: keep lg2 finite,
-            // the row statistic of -inf or the bounds check at the end removes them)
-            const float l2 = lg2(fmaxf(nz[cc], 1e-30f));
-            const float x = fmaf(__uint_as_float(u[cc]), scale, fmaf(l2, neg_inv_tau, lv[e]));
-            const float pr = cc < first_visible ? 0.f : ex2(x);
-            acc[e] += pr;
+            for (int e = 0; e < 4; ++e) {
+              const int cc = g * 4 + e;
+              // (rows and keys past the tensor's end are zero-filled by the copy: keep lg2 finite,
+              // the row statistic of -inf or the bounds check at the end removes them)
+              const float l2 = lg2(fmaxf(nz[cc], 1e-30f));
+              const float x = fmaf(__uint_as_float(u[cc]), scale, fmaf(l2, neg_inv_tau, lv[e]));
+              const float pr = cc < first_visible ? 0.f : ex2(x);
+              acc[e] += pr;
+            }
           }
         }
+        if (!ok) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.q_empty[st]));
       }
-      if (!ok) break;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars.q_empty[st]));
+      cg0 += static_cast<uint32_t>(n_steps);
+      part_s[sgm][sub][wq * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
-    part_s[sub][wq * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     if (!ok) *abortp = 1u;
   }
 
@@ -816,12 +866,15 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
   if (warp >= kUtilWarps && ((warp - kUtilWarps) >> 2) == 0 && !*abortp) {
     const int k_in_tile = (warp & 3) * 32 + lane;
-    const int key = kv0 + k_in_tile;
-    if (key < p.Skv) {
-      const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
-      const float v = (part_s[0][k_in_tile] + part_s[1][k_in_tile]) + (part_s[2][k_in_tile] + part_s[3][k_in_tile]);
-      const size_t slab = static_cast<size_t>(qc) * bh_count * p.Skv;
-      (p.n_qchunks > 1 ? p.part + slab : p.score)[o] = v;
+    for (int sgm = 0; sgm < n_seg; ++sgm) {
+      const int key = kts[sgm] * kTile + k_in_tile;
+      if (key < p.Skv) {
+        const size_t o = (static_cast<size_t>(b) * p.H + h) * p.Skv + key;
+        const float v = (part_s[sgm][0][k_in_tile] + part_s[sgm][1][k_in_tile]) +
+                        (part_s[sgm][2][k_in_tile] + part_s[sgm][3][k_in_tile]);
+        const size_t slab = static_cast<size_t>(qc) * bh_count * p.Skv;
+        (p.n_qchunks > 1 ? p.part + slab : p.score)[o] = v;
+      }
     }
   }
 }
@@ -1185,8 +1238,8 @@ cudaError_t launch_col_scores(const CUtensorMap& mq, const CUtensorMap& mk, cons
     auto nk = s.bf16 ? kf_col_tma_kernel<true> : kf_col_tma_kernel<false>;
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(nk), kNzSmemBytes);
     if (e != cudaSuccess) return e;
-    const int n_kt = (s.Skv + kTile - 1) / kTile;
-    e = launch_dependent(nk, dim3(static_cast<unsigned>(n_kt) * p.n_qchunks * s.B * s.H), dim3(kThreads), kNzSmemBytes,
+    const int n_pairs = ((s.Skv + kTile - 1) / kTile + 1) / 2;  // a CTA works through two key tiles
+    e = launch_dependent(nk, dim3(static_cast<unsigned>(n_pairs) * p.n_qchunks * s.B * s.H), dim3(kThreads), kNzSmemBytes,
                          stream, mq, mk, mn, p);
     count_launch();
   } else
