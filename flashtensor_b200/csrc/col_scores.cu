@@ -539,13 +539,14 @@ col_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // The operand is read exactly once and is nine tenths of this pass's traffic; a thread that owns a
 // key (the transposed layout the MMA gives) would read its column of it with scalar loads, one
 // round trip to L2 or DRAM per 32 logits.  Here a CTA owns ONE key tile, which leaves shared
-// memory for a ring of noise pieces [64 queries x 128 keys] f32 (four 128-byte-swizzled boxes of
-// 32 keys, as in the row pass); two pieces are in flight while the third is consumed.  The sixteen
+// memory for a ring of four noise pieces [64 queries x 128 keys] f32 (four 128-byte-swizzled boxes
+// of 32 keys each, as in the row pass); three pieces are in flight while one is consumed (with two
+// in flight the pass ran at 4.7 TB/s: 64 KB per SM do not cover the latency of DRAM under load).  The sixteen
 // key warps are (TMEM lane quarter) x (16 of a piece's 64 queries).  A CTA takes two key tiles in
 // turn (see the comment on segments in the kernel).
 // ---------------------------------------------------------------------------------------------
 constexpr int kNzQStages = 2;
-constexpr int kNzStages = 3;
+constexpr int kNzStages = 4;
 constexpr int kNzRows = 64;                                  // queries per noise piece
 constexpr uint32_t kNzPieceBytes = kNzRows * kTile * 4;      // 32 KB
 constexpr uint32_t kNzBoxBytes = kNzPieceBytes / 4;          // one box: 32 keys x 64 queries
@@ -565,7 +566,6 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) NzBars bars;
   __shared__ __align__(16) float lse_s[kNzQStages][kTile];  // minus the row statistic
-  __shared__ float part_s[2][4][kTile];                     // [segment][which 16 queries][key]
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
 
@@ -574,6 +574,10 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const uint32_t sK = smem_base;
   const uint32_t sQ = smem_base + kTileBytes;
   const uint32_t sN = sQ + kNzQStages * kTileBytes;
+  // [segment][which 16 queries][key] partial sums, written after a warp's last step: they take the
+  // place of the first Q stage, which nothing reads any more by then (every MMA has retired
+  // before the step that waits for it is over, and no copy into the stage is outstanding)
+  float (*part_s)[4][kTile] = reinterpret_cast<float (*)[4][kTile]>(smem_raw + (sQ - smem_u32(smem_raw)));
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -645,9 +649,9 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (whole warp)
     // Order of issue within a segment: K; Q of its first step; then per step its two noise
-    // pieces, then Q of the next step.  A noise piece waits for the piece three before it to have
+    // pieces, then Q of the next step.  A noise piece waits for the piece four before it to have
     // been consumed, Q of step c + 1 for step c - 1 to be over: while the key warps work on step
-    // c - 1 the two pieces of step c are in flight, and Q of step c + 1 arrives during step c.
+    // c the pieces of step c + 1 are in flight, and Q of step c + 1 arrives as well.
     const float* lse_row = p.lse2 + (static_cast<size_t>(b) * p.H + h) * p.Sq;
     bool ok = true;
     if (p.chained) griddep_wait();  // the row statistic is the output of the kernel ahead
@@ -789,6 +793,7 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     bool ok = true;
     uint32_t nc = 0;   // noise pieces consumed
     uint32_t cg0 = 0;  // steps of the segments before this one
+    float seg_sum[2] = {0.f, 0.f};
     for (int sgm = 0; sgm < n_seg; ++sgm) {
       int kv0, i_begin, n_steps;
       segment(sgm, kv0, i_begin, n_steps);
@@ -853,8 +858,11 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (lane == 0) mbar_arrive(smem_u32(&bars.q_empty[st]));
       }
       cg0 += static_cast<uint32_t>(n_steps);
-      part_s[sgm][sub][wq * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      seg_sum[sgm] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
+    // (only now: the partial sums lie over a Q stage, which the second segment still uses)
+    part_s[0][sub][wq * 32 + lane] = seg_sum[0];
+    part_s[1][sub][wq * 32 + lane] = seg_sum[1];
     if (!ok) *abortp = 1u;
   }
 
