@@ -892,12 +892,17 @@ kf_col_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // One CTA per 128 query rows; one thread per row; K tiles stream through a ring.
 // kNoiseTma: the [128 x 128] f32 noise tile of every step is staged in shared memory by TMA
 // (four 128-byte-swizzled boxes of 32 keys) -- the kernel is bound by that 2 GB read, and a
-// thread walking its own row in global memory wastes most of every sector.  The plain variant
-// (direct loads) serves noise tensors whose strides TMA cannot describe.
+// thread walking its own row in global memory wastes most of every sector.  The boxes of two steps
+// form a ring of eight with a barrier pair each: a box goes back to the producer as soon as the
+// four warps that read it have it in registers, so the first boxes of the step after next are
+// under way while the second half of the current step is computed (what is in flight per SM is
+// what bounds a pass that reads everything once).  The plain variant (direct loads) serves noise
+// tensors whose strides TMA cannot describe.
 // ---------------------------------------------------------------------------------------------
 constexpr int kRsThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 rows (two per 32 rows: columns 0..63 / 64..127)
 constexpr uint32_t kNoiseTileBytes = 128 * 128 * 4;
-template <int kNoise> struct RsCfg {  // kNoise 1: the noise tile shares the stage with K
+constexpr uint32_t kNoiseBoxBytes = kNoiseTileBytes / 4;
+template <int kNoise> struct RsCfg {  // kNoise 1: two K stages, then eight noise boxes
   static constexpr bool kNoiseTma = kNoise == 1;
   static constexpr int kStages = kNoise == 0 ? 4 : 2;  // seeded: small enough for two CTAs per SM
   static constexpr uint32_t kStageBytes = kTileBytes + (kNoiseTma ? kNoiseTileBytes : 0);
@@ -908,6 +913,7 @@ struct RsBars {
   uint64_t q_full;
   uint64_t k_full[4], k_empty[4];
   uint64_t s_full[2], s_empty[2];
+  uint64_t n_full[8], n_empty[8];  // staged noise: one pair per box of the ring
 };
 
 // kNoise: 0 noise operand read directly, 1 noise operand staged by TMA, 2 seeded noise
@@ -925,7 +931,8 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base;
-  const uint32_t sStage = smem_base + kTileBytes;  // per stage: K tile, then (TMA variant) the noise tile
+  const uint32_t sStage = smem_base + kTileBytes;             // the K stages
+  const uint32_t sNoise = sStage + kStages * kTileBytes;      // (TMA variant) eight boxes [128 rows x 32 keys] f32
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile uint32_t* abortp = &abort_s;
@@ -951,8 +958,13 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_init(smem_u32(&bars.q_full), 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(smem_u32(&bars.k_full[i]), 1);
-      // the MMA commit, plus (TMA variant) one arrival per row warp once the noise has been read
-      mbar_init(smem_u32(&bars.k_empty[i]), kNoiseTma ? 9 : 1);
+      mbar_init(smem_u32(&bars.k_empty[i]), 1);  // the MMA commit
+    }
+    if constexpr (kNoiseTma) {
+      for (int i = 0; i < 8; ++i) {
+        mbar_init(smem_u32(&bars.n_full[i]), 1);
+        mbar_init(smem_u32(&bars.n_empty[i]), 4);  // the four warps that read the box
+      }
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars.s_full[i]), 1);
@@ -986,15 +998,28 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           break;
         }
         const uint32_t bar = smem_u32(&bars.k_full[st]);
-        const uint32_t base = sStage + st * Cfg::kStageBytes;
-        mbar_expect_tx(bar, Cfg::kStageBytes);
+        const uint32_t base = sStage + st * kTileBytes;
+        mbar_expect_tx(bar, kTileBytes);
         tma_load_4d(base, &map_k, bar, 0, h / p.group, j * kTile, b);
         tma_load_4d(base + kHalfBytes, &map_k, bar, 64, h / p.group, j * kTile, b);
         if constexpr (kNoiseTma) {
+          // the first box of either column half first; step j uses ring slots (j & 1) * 4 ..
+          bool good = true;
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4)  // (read once: first to leave L2)
-            tma_load_4d_hint(base + kTileBytes + c4 * (kNoiseTileBytes / 4), &map_n, bar, j * kTile + c4 * 32, q0,
-                             h, b, l2_policy_evict_first());
+          for (int x = 0; x < 4 && good; ++x) {
+            const int c4 = (x & 1) * 2 + (x >> 1);  // 0, 2, 1, 3
+            const int slot = (j & 1) * 4 + c4;
+            if (j >= 2 && !mbar_wait(smem_u32(&bars.n_empty[slot]), ((j >> 1) - 1) & 1, abortp)) {
+              record_timeout(p.status, 36);
+              good = false;
+              break;
+            }
+            const uint32_t nbar = smem_u32(&bars.n_full[slot]);
+            mbar_expect_tx(nbar, kNoiseBoxBytes);
+            tma_load_4d_hint(sNoise + slot * kNoiseBoxBytes, &map_n, nbar, j * kTile + c4 * 32, q0, h, b,
+                             l2_policy_evict_first());  // (read once: first to leave L2)
+          }
+          if (!good) break;
         }
       }
     }
@@ -1018,7 +1043,7 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           if (!ok) break;
         }
         tc_fence_after_sync();
-        const uint64_t kdesc = umma_smem_desc_sw128(sStage + st * Cfg::kStageBytes, 16, 1024);
+        const uint64_t kdesc = umma_smem_desc_sw128(sStage + st * kTileBytes, 16, 1024);
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -1052,25 +1077,28 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int buf = j & 1;
-      const int st = j % kStages;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.s_full[buf]), (j >> 1) & 1, abortp));
       if (!ok) { if (lane == 0) record_timeout(p.status, 35); break; }
       tc_fence_after_sync();
       const int thr = lim - j * kTile;  // columns > thr are masked
-      const uint8_t* noise_tile = smem_gen + kTileBytes + st * Cfg::kStageBytes + kTileBytes;
 #pragma unroll
       for (int c4 = half * 2; c4 < half * 2 + 2; ++c4) {
         uint32_t u[32];
         tmem_ld32(tbase + lane_base + buf * 128 + c4 * 32, u);
         float er[32];
         if constexpr (kNoiseTma) {
+          const int slot = (j & 1) * 4 + c4;
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.n_full[slot]), (j >> 1) & 1, abortp));
+          if (!ok) { if (lane == 0) record_timeout(p.status, 37); break; }
           // this row's 32 noise values of box c4: eight swizzled 16-byte chunks
-          const uint8_t* box = noise_tile + c4 * (kNoiseTileBytes / 4);
+          const uint8_t* box = smem_gen + (sNoise - smem_base) + slot * kNoiseBoxBytes;
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
             const float4 v = *reinterpret_cast<const float4*>(box + sw128_offset(r_in_tile, ch));
             er[ch * 4 + 0] = v.x; er[ch * 4 + 1] = v.y; er[ch * 4 + 2] = v.z; er[ch * 4 + 3] = v.w;
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars.n_empty[slot]));  // in registers: the box may be refilled
         } else if constexpr (kNoise == 0) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) er[e] = __ldg(er_row + min(j * kTile + c4 * 32 + e, p.Skv - 1));
@@ -1100,12 +1128,9 @@ kf_rowstat_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           m = m_new;
         }
       }
+      if (!ok) break;
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bars.s_empty[buf]));
-      if constexpr (kNoiseTma) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars.k_empty[st]));
-      }
     }
     // hand-over through the Q tile's shared memory: every MMA that read it has retired (this thread
     // has seen the last S tile), and the variant with the staged noise has no other room left
